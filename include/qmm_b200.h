@@ -1,0 +1,192 @@
+/*
+ * qmm_b200.h — C ABI of the B200 (sm_100a) weight-quantized linear kernels.
+ *
+ * The reference (pytorch/xla) has no C ABI for this path: its operator is a PyTorch
+ * dispatcher op whose arithmetic runs inside XLA or a TPU Pallas kernel.  The entry points
+ * below are what a binding for that operator calls instead; each one names the reference
+ * interface it stands in for (paths are inside the pytorch/xla tree).
+ *
+ * Conventions
+ *   - Every pointer is DEVICE memory owned by the caller, except where a parameter is
+ *     documented as a host pointer.  Nothing here allocates, frees or synchronises; all work
+ *     is enqueued on `stream` (a cudaStream_t passed as void*; NULL = the legacy default stream).
+ *   - Matrices are dense row-major.  M = number of activation rows (product of x's leading
+ *     dims), K = in_features, N = out_features, S = K / block_size.
+ *   - Every function returns a qmm_status; 0 is success.  No exception or abort crosses the ABI.
+ *     qmm_last_error_string() gives a per-thread description of the last failure.
+ *   - There is no CPU fallback: a call that cannot run on the current device fails with a status.
+ *   - `variant` picks the kernel family; QMM_VARIANT_AUTO chooses by shape.  A variant that
+ *     cannot take the given shape fails with QMM_ERR_UNSUPPORTED rather than running another one.
+ */
+#ifndef QMM_B200_H_
+#define QMM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QMM_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define QMM_API __attribute__((visibility("default")))
+#else
+#define QMM_API
+#endif
+
+typedef enum qmm_dtype {
+  QMM_F32 = 0,
+  QMM_BF16 = 1,
+  QMM_F16 = 2,
+} qmm_dtype;
+
+typedef enum qmm_status {
+  QMM_OK = 0,
+  QMM_ERR_BAD_SHAPE = 1,   /* a dimension is negative, zero where it may not be, or inconsistent */
+  QMM_ERR_UNSUPPORTED = 2, /* valid request that the chosen variant / this build cannot run */
+  QMM_ERR_MISALIGNED = 3,  /* a pointer or row pitch breaks the alignment the variant needs */
+  QMM_ERR_LAUNCH = 4,      /* the CUDA runtime rejected a launch or a descriptor */
+  QMM_ERR_WORKSPACE = 5,   /* workspace missing or smaller than qmm_workspace_size() says */
+  QMM_ERR_NULL = 6,        /* a required pointer is NULL */
+  QMM_ERR_DEVICE = 7,      /* current device is not sm_100 or the driver lacks a needed entry */
+  QMM_ERR_TIMEOUT = 8,     /* a bounded device-side wait gave up (see qmm_device_error_flag) */
+} qmm_status;
+
+typedef enum qmm_variant {
+  QMM_VARIANT_AUTO = 0,
+  QMM_VARIANT_GENERIC = 1, /* any shape, any alignment; one thread per output element */
+  QMM_VARIANT_GEMV = 2,    /* decode: warp-per-row, 128-bit weight loads, M <= 8 */
+  QMM_VARIANT_TCGEN05 = 3, /* TMA -> shared memory -> tcgen05.mma with TMEM accumulators */
+} qmm_variant;
+
+typedef enum qmm_op {
+  QMM_OP_W8A16_PERCHANNEL = 0,
+  QMM_OP_BLOCKWISE_SBN = 1,
+  QMM_OP_W4A16_BLOCKWISE_PACKED = 2,
+  QMM_OP_W8A8_PERCHANNEL = 3,
+  QMM_OP_W4A16_PERCHANNEL_PACKED = 4,
+} qmm_op;
+
+QMM_API int qmm_abi_version(void);
+QMM_API const char* qmm_status_string(int status);
+QMM_API const char* qmm_last_error_string(void);
+
+/*
+ * Per-channel weight-only linear:  out[m,n] = (sum_k x[m,k] * w[n,k]) * scale[n] - (sum_k x[m,k]) * zp[n].
+ * Replaces: torch.ops.xla.quantized_matmul with block_size == -1, quantize_activation == False
+ *   (torch_xla/experimental/xla_quantized_matmul.py:76-114 XLA key, :139-159 CPU key; the
+ *   mixed bf16 x s8 dot it lowers to: torch_xla/csrc/xla_lower_util.cpp:477-481).
+ * w: int8 [N,K] (int4 values in an int8 container are the same call); scale: f32 [N];
+ * zp: f32 [N] in scaled units, or NULL.  Accumulation is fp32; the scale is applied once, after it.
+ */
+QMM_API int qmm_w8a16_perchannel(const void* x, int x_dtype, const int8_t* w, const float* scale,
+                         const float* zp, void* out, int out_dtype, int64_t M, int64_t N,
+                         int64_t K, int variant, void* stream);
+
+/*
+ * Blockwise weight-only linear on the reference's own weight layout [S, block_size, N] (N minor):
+ *   out[m,n] = sum_b scale[b,n] * (sum_c x[m,b*bs+c] * w[b,c,n]) - sum_b (sum_c x[m,b*bs+c]) * zp[b,n].
+ * Replaces: torch.ops.xla.quantized_matmul with block_size > 0
+ *   (xla_quantized_matmul.py:115-124 and :160-170; layout check :27-53).
+ * w: int8 [S,bs,N]; scale, zp: f32 [S,N]; zp may be NULL.
+ */
+QMM_API int qmm_blockwise_sbn(const void* x, int x_dtype, const int8_t* w, const float* scale,
+                      const float* zp, void* out, int out_dtype, int64_t M, int64_t N, int64_t K,
+                      int64_t block_size, int variant, void* stream);
+
+/*
+ * Blockwise weight-only linear on int4 weights packed two per byte along K:
+ * wp: uint8 [N, K/2], byte j of row n holds k=2j in its low nibble and k=2j+1 in its high
+ * nibble, two's complement.  scale, zp: f32 [S,N] as above.  Same formula as qmm_blockwise_sbn.
+ * Replaces: the int4 route of the same op, where the reference re-materialises the weight as an
+ *   S4 literal on every call (xla_quantized_matmul.py:101-103; torch_xla/csrc/ops/cast_int4.cpp:14-39).
+ *   The packed layout itself has no counterpart in the reference (it stores int4 unpacked).
+ */
+QMM_API int qmm_w4a16_blockwise_packed(const void* x, int x_dtype, const uint8_t* wp, const float* scale,
+                               const float* zp, void* out, int out_dtype, int64_t M, int64_t N,
+                               int64_t K, int64_t block_size, int variant, void* stream);
+
+/*
+ * Per-channel weight-only linear on packed int4 weights (wp: uint8 [N,K/2], nibble order as above;
+ * scale, zp: f32 [N]).  Same formula as qmm_w8a16_perchannel.
+ * Replaces: the int4_weight=True route of the per-channel op (xla_quantized_matmul.py:101-114).
+ */
+QMM_API int qmm_w4a16_perchannel_packed(const void* x, int x_dtype, const uint8_t* wp, const float* scale,
+                                const float* zp, void* out, int out_dtype, int64_t M, int64_t N,
+                                int64_t K, int variant, void* stream);
+
+/*
+ * Per-token dynamic activation quantizer:
+ *   amax = max_k |x[m,k]|; s = amax / 127 (rounded to x's dtype); xq = rint(x / s) (quotient
+ *   rounded to x's dtype first) -> int8.
+ * Replaces: _quantize_tensor (xla_quantized_matmul.py:56-73) and _quantize_array
+ *   (torch_xla/experimental/pallas_kernels/quantized_matmul_kernel.py:10-18).
+ * saturate != 0 clamps to [-128,127] (what an XLA device does); saturate == 0 wraps a pre-cast
+ * +128 to -128 like the reference's eager CPU conversion.  x_scale: f32 [M] (exact upcast of the
+ * scale); xq_rowsum: int32 [M] = sum_k xq[m,k], or NULL.
+ */
+QMM_API int qmm_quantize_activation(const void* x, int x_dtype, int8_t* xq, float* x_scale,
+                            int32_t* xq_rowsum, int64_t M, int64_t K, int saturate, void* stream);
+
+/*
+ * W8A8 contraction with int32 accumulation and the fp32 dequant epilogue:
+ *   acc[m,n] = sum_k xq[m,k] * w[n,k]                                  (exact, int32)
+ *   out[m,n] = ((float)acc * w_scale[n] - (float)xq_rowsum[m] * zp[n]) * x_scale[m]
+ * Replaces: _xla_dot_general(int8,int8 -> int32) (torch_xla/csrc/ops/dot_general.cpp:16-37,
+ *   xla_quantized_matmul.py:110-111), the CPU twin F.linear(int32,int32) (:153-158), the
+ *   scale multiplications (:114,:134-135 / :159,:181-182) and the Pallas tile body
+ *   (quantized_matmul_kernel.py:101-121).
+ * acc_out (int32 [M,N]) and out may each be NULL, not both.  zp needs xq_rowsum.
+ */
+QMM_API int qmm_w8a8_gemm(const int8_t* xq, const int8_t* w, const float* w_scale, const float* zp,
+                  const float* x_scale, const int32_t* xq_rowsum, int32_t* acc_out, void* out,
+                  int out_dtype, int64_t M, int64_t N, int64_t K, int variant, void* stream);
+
+/*
+ * The whole quantize_activation=True op: quantizer + contraction + epilogue.
+ * Replaces: torch.ops.xla.quantized_matmul(..., quantize_activation=True)
+ *   (xla_quantized_matmul.py:107-114,:134-135) and torch.ops.xla.quantized_matmul_int8
+ *   (torch_xla/experimental/custom_kernel.py:1066-1106, :1742-1761).
+ * workspace: qmm_workspace_size(QMM_OP_W8A8_PERCHANNEL, M, N, K) bytes of device memory, 256-byte
+ * aligned, holding the quantized activations between the two kernels.
+ */
+QMM_API int qmm_w8a8_perchannel(const void* x, int x_dtype, const int8_t* w, const float* w_scale,
+                        const float* zp, void* out, int out_dtype, int64_t M, int64_t N,
+                        int64_t K, int saturate, int variant, void* workspace,
+                        size_t workspace_bytes, void* stream);
+
+/* Bytes of caller-provided scratch an op needs for the given shape (0 if none). */
+QMM_API size_t qmm_workspace_size(int op, int64_t M, int64_t N, int64_t K);
+
+/*
+ * int4 packing (device to device).  Values must lie in [-8,7].
+ *   qmm_pack_int4_nk : int8 [N,K]      -> uint8 [N,K/2]
+ *   qmm_pack_int4_sbn: int8 [S,bs,N]   -> uint8 [N,K/2]   (K = S*bs)
+ *   qmm_unpack_int4_nk: uint8 [N,K/2]  -> int8 [N,K]
+ * Replaces: _xla_cast_int4 / the CastInt4 IR node (torch_xla/csrc/ops/cast_int4.cpp:14-39), which
+ *   narrows an int8 container to 4-bit storage for the device.
+ */
+QMM_API int qmm_pack_int4_nk(const int8_t* w, uint8_t* wp, int64_t N, int64_t K, void* stream);
+QMM_API int qmm_pack_int4_sbn(const int8_t* w, uint8_t* wp, int64_t S, int64_t block_size, int64_t N,
+                      void* stream);
+QMM_API int qmm_unpack_int4_nk(const uint8_t* wp, int8_t* w, int64_t N, int64_t K, void* stream);
+
+/*
+ * Device-side error word of the current device.  Kernels that wait on hardware barriers give up
+ * after a bounded number of polls and record a non-zero code here instead of hanging.
+ * Reads the word back (this call synchronises `stream`), stores it in *flag (HOST pointer) and
+ * clears it.  Returns QMM_ERR_TIMEOUT if it was non-zero.
+ */
+QMM_API int qmm_device_error_flag(uint32_t* flag, void* stream);
+
+/* Name of the kernel family the AUTO heuristic picks (static string, for logs and tests). */
+QMM_API const char* qmm_variant_for(int op, int64_t M, int64_t N, int64_t K, int64_t block_size,
+                            int has_zp);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* QMM_B200_H_ */

@@ -1,0 +1,60 @@
+"""The C-ABI library loads on a machine without a GPU and exports every symbol the header declares."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from xla_b200 import _build, _capi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+  text = open(os.path.join(ROOT, "include", "qmm_b200.h")).read()
+  return sorted(set(re.findall(r"QMM_API\s+[\w\s\*]+?\b(qmm_\w+)\s*\(", text)))
+
+
+def test_library_is_built_in_tree():
+  assert os.path.exists(_build.LIB_PATH), "run `python -m xla_b200._build`"
+  assert _build.LIB_PATH.startswith(ROOT)
+
+
+def test_every_declared_symbol_is_exported_and_bound():
+  names = declared_symbols()
+  assert len(names) >= 16
+  L = ctypes.CDLL(_build.LIB_PATH)
+  for n in names:
+    assert hasattr(L, n), f"{n} declared in include/qmm_b200.h but not exported"
+  assert set(names) == set(_capi.SIGNATURES), "ctypes table and header disagree"
+
+
+def test_version_and_status_strings():
+  L = _capi.lib()
+  assert L.qmm_abi_version() == 1
+  assert L.qmm_status_string(0) == b"ok"
+  assert L.qmm_status_string(2) == b"unsupported"
+  assert L.qmm_status_string(99) == b"unknown status"
+
+
+def test_argument_errors_need_no_gpu():
+  L = _capi.lib()
+  # negative dimension
+  assert L.qmm_w8a16_perchannel(None, 1, None, None, None, None, 1, -1, 4, 4, 0, None) == 1
+  assert b"negative" in L.qmm_last_error_string()
+  # bad dtype code
+  assert L.qmm_w8a16_perchannel(None, 7, None, None, None, None, 1, 1, 4, 4, 0, None) == 2
+  # NULL output with work to do
+  assert L.qmm_w8a16_perchannel(None, 1, None, None, None, None, 1, 1, 4, 4, 0, None) == 6
+  # empty problem is a no-op success
+  assert L.qmm_w8a16_perchannel(None, 1, None, None, None, None, 1, 0, 4, 4, 0, None) == 0
+  # block size must divide K
+  assert L.qmm_blockwise_sbn(None, 1, None, None, None, None, 1, 0, 4, 6, 4, 0, None) == 1
+  assert b"divisible by block_size" in L.qmm_last_error_string()
+  # workspace size: xq + scales + row sums, 256-byte granules
+  assert L.qmm_workspace_size(_capi.OP_W8A8_PERCHANNEL, 2048, 4096, 4096) == 2048 * 4096 + 2 * 8192
+  assert L.qmm_workspace_size(_capi.OP_W8A16_PERCHANNEL, 16, 4096, 4096) == 0
+  with pytest.raises(AssertionError):
+    _capi.check(1)
+  with pytest.raises(NotImplementedError):
+    _capi.check(2)

@@ -1,0 +1,106 @@
+"""Host-side mirror of the reference interface: schemas, validators, module, dispatch; no GPU."""
+import pytest
+import torch
+
+import xla_b200
+from xla_b200 import quantized_matmul as qm
+
+
+def test_schemas_match_the_reference_byte_for_byte():
+  # torch_xla/experimental/xla_quantized_matmul.py:7-9
+  assert str(torch.ops.xla.quantized_matmul.default._schema) == (
+      "xla::quantized_matmul(Tensor x, Tensor w, Tensor scale, Tensor? zero_point=None, int? block_size=-1, "
+      "bool? int4_weight=False, bool? quantize_activation=False) -> Tensor")
+  # torch_xla/experimental/custom_kernel.py:1742-1744
+  assert str(torch.ops.xla.quantized_matmul_int8.default._schema) == (
+      "xla::quantized_matmul_int8(Tensor x, Tensor w, Tensor scalar, Tensor? zero_point=None, "
+      "Tensor? quant_block_size=None, bool quantize_activation=False, int? batch_block_size=None, "
+      "int? out_block_size=None, int? in_block_size=None) -> Tensor")
+  s = str(torch.ops.xla_b200.quantized_matmul_packed.default._schema)
+  assert "weight_is_packed" in s and "block_size" in s and "quantize_activation" in s
+
+
+def test_cpu_tensors_fail_loudly():
+  x, w, s = torch.zeros(2, 8), torch.zeros(4, 8, dtype=torch.int8), torch.ones(4)
+  with pytest.raises(NotImplementedError):
+    torch.ops.xla.quantized_matmul(x, w, s)
+  with pytest.raises(NotImplementedError):
+    torch.ops.xla.quantized_matmul_int8(x, w, s)
+  with pytest.raises(RuntimeError, match="no CPU path"):
+    qm.quantized_matmul_cuda(x, w, s)
+
+
+def test_meta_kernels_give_reference_shapes_and_dtypes():
+  meta = lambda *s, dtype=torch.float32: torch.empty(*s, dtype=dtype, device="meta")
+  x = meta(2, 3, 64, dtype=torch.bfloat16)
+  w = meta(16, 64, dtype=torch.int8)
+  assert torch.ops.xla.quantized_matmul(x, w, meta(16)).shape == (2, 3, 16)
+  # type promotion decides the output dtype (bf16 activations, fp32 scaler -> fp32)
+  assert torch.ops.xla.quantized_matmul(x, w, meta(16)).dtype == torch.float32
+  assert torch.ops.xla.quantized_matmul(x, w, meta(16, dtype=torch.bfloat16)).dtype == torch.bfloat16
+  wb = meta(4, 16, 24, dtype=torch.int8)
+  assert torch.ops.xla.quantized_matmul(x, wb, meta(4, 24), block_size=16).shape == (2, 3, 24)
+  # the Pallas-registry op always returns x.dtype
+  x2 = meta(5, 64, dtype=torch.bfloat16)
+  o = torch.ops.xla.quantized_matmul_int8(x2, w, meta(16), quantize_activation=True)
+  assert o.shape == (5, 16) and o.dtype == torch.bfloat16
+  o = torch.ops.xla_b200.quantized_matmul_packed(x, meta(16, 32, dtype=torch.uint8), meta(4, 16), block_size=16,
+                                                int4_weight=True, weight_is_packed=True, out_dtype=torch.bfloat16)
+  assert o.shape == (2, 3, 16) and o.dtype == torch.bfloat16
+
+
+def test_validators_raise_assertion_errors_with_reference_text():
+  w = torch.zeros(8, 5, dtype=torch.int8)
+  s = torch.ones(8)
+  qm._check_per_channel_quant_weight_dtype_shapes(5, 8, w, s, None)
+  with pytest.raises(AssertionError, match="Weight dtype is expected to be torch.int8"):
+    qm._check_per_channel_quant_weight_dtype_shapes(5, 8, w.float(), s, None)
+  with pytest.raises(AssertionError, match="Weight tensor is expected to be 2D, got 3D"):
+    qm._check_per_channel_quant_weight_dtype_shapes(5, 8, w[None], s, None)
+  with pytest.raises(AssertionError, match=r"Weight shape is expected to be \[output_dim, input_dim\]"):
+    qm._check_per_channel_quant_weight_dtype_shapes(6, 8, w, s, None)
+  with pytest.raises(AssertionError, match="weight scaler shape is expect to be"):
+    qm._check_per_channel_quant_weight_dtype_shapes(5, 8, w, torch.ones(7), None)
+  wb = torch.zeros(3, 2, 8, dtype=torch.int8)
+  sb = torch.ones(3, 8)
+  qm._check_blockwise_quant_weight_dtype_shapes(6, 8, 2, wb, sb, sb)
+  with pytest.raises(AssertionError, match="input_dim should be divisible by block_size"):
+    qm._check_blockwise_quant_weight_dtype_shapes(7, 8, 2, wb, sb, None)
+  with pytest.raises(AssertionError, match="Weight tensor is expected to be 3D"):
+    qm._check_blockwise_quant_weight_dtype_shapes(6, 8, 2, wb[0], sb, None)
+  with pytest.raises(AssertionError, match="weight scaler is expected to be 2D"):
+    qm._check_blockwise_quant_weight_dtype_shapes(6, 8, 2, wb, sb[0], None)
+  with pytest.raises(AssertionError, match="zero_point shape is expect to be"):
+    qm._check_blockwise_quant_weight_dtype_shapes(6, 8, 2, wb, sb, torch.ones(2, 8))
+
+
+def test_module_mirrors_reference_buffers(golden):
+  sym = xla_b200.XlaQuantizedLinear(32, 16, is_symmetric=True)
+  asym = xla_b200.XlaQuantizedLinear(32, 16)
+  assert sorted(sym.state_dict().keys()) == list(golden.np("module/state_keys_sym"))
+  assert sorted(asym.state_dict().keys()) == list(golden.np("module/state_keys_asym"))
+  assert sym.weight.dtype == torch.int8 and tuple(sym.weight.shape) == (16, 32)
+  assert sym.weight_scaler.shape == (16,) and sym.zero_point is None
+  with pytest.raises(AssertionError):
+    sym.load_quantized_weight(torch.zeros(16, 31, dtype=torch.int8), torch.ones(16))
+  blk = xla_b200.XlaQuantizedLinear(32, 16, is_symmetric=True, block_size=8, int4_weight=True)
+  blk.load_quantized_weight(torch.zeros(4, 8, 16, dtype=torch.int8), torch.ones(4, 16))
+  assert tuple(blk.weight.shape) == (4, 8, 16)
+  # state round trip keeps the reference's names
+  sym2 = xla_b200.XlaQuantizedLinear(32, 16, is_symmetric=True)
+  sym2.load_state_dict(sym.state_dict())
+
+
+def test_blockwise_rejects_activation_quantization_before_touching_the_gpu():
+  x = torch.zeros(2, 6, device="meta")
+  with pytest.raises(Exception):
+    qm.quantized_matmul_cuda(x, torch.zeros(3, 2, 8, dtype=torch.int8), torch.ones(3, 8), block_size=2,
+                             quantize_activation=True)
+
+
+def test_variant_heuristic_is_shape_only():
+  L = xla_b200._capi.lib()
+  assert L.qmm_variant_for(xla_b200._capi.OP_W8A16_PERCHANNEL, 1, 4096, 4096, 0, 0) == b"gemv"
+  assert L.qmm_variant_for(xla_b200._capi.OP_W8A16_PERCHANNEL, 3, 8, 5, 0, 0) == b"generic"
+  assert L.qmm_variant_for(xla_b200._capi.OP_W4A16_BLOCKWISE_PACKED, 1, 14336, 4096, 128, 0) == b"gemv"
+  assert L.qmm_variant_for(xla_b200._capi.OP_W8A8_PERCHANNEL, 2048, 4096, 4096, 0, 0) == b"tcgen05"

@@ -102,3 +102,28 @@ def test_empty_inputs():
   s = torch.ones(4)
   assert qo.quantized_matmul(x, w, s).shape == (0, 4)
   assert qo.quantized_matmul(x, w, s, quantize_activation=True).shape == (0, 4)
+
+
+def test_torch_port_matches_reference_outputs(golden):
+  """oracle/torch_port.py (the timed CPU baseline) reproduces the reference's outputs exactly."""
+  from oracle import torch_port as tp
+  for tag in ("bf16", "f32"):
+    k = f"w8a8_{tag}"
+    x = golden.t(k + "/x", bf16=(tag == "bf16"))
+    w, s, zp = golden.t(k + "/w"), golden.t(k + "/scale"), golden.t(k + "/zp")
+    assert torch.equal(tp.quantized_matmul_cpu(x, w, s, quantize_activation=True), golden.t(k + "/out"))
+    assert torch.allclose(tp.quantized_matmul_cpu(x, w, s, zp, quantize_activation=True), golden.t(k + "/out_zp"),
+                          rtol=1e-6, atol=1e-6)
+  for tag in ("bf16", "f32", "f32b"):
+    k = f"pc_{tag}"
+    x = golden.t(k + "/x", bf16=(tag == "bf16"))
+    w, s, zp = golden.t(k + "/w"), golden.t(k + "/scale"), golden.t(k + "/zp")
+    assert torch.allclose(tp.quantized_matmul_cpu(x, w, s), golden.t(k + "/out"), rtol=1e-5, atol=1e-5)
+    assert torch.allclose(tp.quantized_matmul_cpu(x, w, s, zp), golden.t(k + "/out_zp"), rtol=1e-5, atol=1e-5)
+  for tag in ("kat", "b128"):
+    k = f"bw_{tag}"
+    x, w, s, zp = golden.t(k + "/x"), golden.t(k + "/w"), golden.t(k + "/scale"), golden.t(k + "/zp")
+    bs = int(golden.np(k + "/block_size"))
+    assert torch.allclose(tp.quantized_matmul_cpu(x, w, s, block_size=bs), golden.t(k + "/out"), rtol=1e-5, atol=1e-5)
+    assert torch.allclose(tp.quantized_matmul_cpu(x, w, s, zp, block_size=bs), golden.t(k + "/out_zp"), rtol=1e-5,
+                          atol=1e-5)

@@ -1,0 +1,18 @@
+"""B200-native drop-in for PyTorch/XLA's weight-quantized linear path.
+
+Importing the package registers ``torch.ops.xla.quantized_matmul``,
+``torch.ops.xla.quantized_matmul_int8`` and ``torch.ops.xla_b200.quantized_matmul_packed`` for the
+CUDA dispatch key.  The kernels live in ``xla_b200/lib/libqmm_b200.so`` (C ABI:
+``include/qmm_b200.h``); build it with ``python -m xla_b200._build``.
+"""
+from . import _capi  # noqa: F401
+from .quantized_matmul import (XlaQuantizedLinear, force_variant, quantize_tensor,  # noqa: F401
+                               set_activation_saturation)
+from . import custom_kernel  # noqa: F401
+from . import packed  # noqa: F401
+from .packed import pack_int4, quantized_matmul_packed, unpack_int4  # noqa: F401
+
+__all__ = [
+    "XlaQuantizedLinear", "force_variant", "quantize_tensor", "set_activation_saturation", "pack_int4",
+    "unpack_int4", "quantized_matmul_packed"
+]

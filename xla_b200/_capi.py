@@ -1,0 +1,96 @@
+"""ctypes binding of libqmm_b200.so (the C ABI declared in include/qmm_b200.h).
+
+The library is loaded from ``xla_b200/lib``; if it is missing, importing this module fails with a
+message that says how to build it.  There is no fallback implementation.
+"""
+import ctypes
+import os
+
+import torch
+
+from . import _build
+
+F32, BF16, F16 = 0, 1, 2
+AUTO, GENERIC, GEMV, TCGEN05 = 0, 1, 2, 3
+OP_W8A16_PERCHANNEL, OP_BLOCKWISE_SBN, OP_W4A16_BLOCKWISE_PACKED, OP_W8A8_PERCHANNEL, OP_W4A16_PERCHANNEL_PACKED = range(5)
+
+VARIANTS = {"auto": AUTO, "generic": GENERIC, "gemv": GEMV, "tcgen05": TCGEN05}
+
+_DTYPES = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
+
+_STATUS_EXC = {1: AssertionError, 2: NotImplementedError, 3: ValueError, 5: ValueError, 6: ValueError}
+
+# name -> (restype, argtypes); every symbol include/qmm_b200.h declares
+_p, _i, _i64, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_size_t
+SIGNATURES = {
+    "qmm_abi_version": (_i, []),
+    "qmm_status_string": (ctypes.c_char_p, [_i]),
+    "qmm_last_error_string": (ctypes.c_char_p, []),
+    "qmm_w8a16_perchannel": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i, _p]),
+    "qmm_w4a16_perchannel_packed": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i, _p]),
+    "qmm_blockwise_sbn": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _p]),
+    "qmm_w4a16_blockwise_packed": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _p]),
+    "qmm_quantize_activation": (_i, [_p, _i, _p, _p, _p, _i64, _i64, _i, _p]),
+    "qmm_w8a8_gemm": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i, _p]),
+    "qmm_w8a8_perchannel": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i, _i, _p, _sz, _p]),
+    "qmm_workspace_size": (_sz, [_i, _i64, _i64, _i64]),
+    "qmm_pack_int4_nk": (_i, [_p, _p, _i64, _i64, _p]),
+    "qmm_pack_int4_sbn": (_i, [_p, _p, _i64, _i64, _i64, _p]),
+    "qmm_unpack_int4_nk": (_i, [_p, _p, _i64, _i64, _p]),
+    "qmm_device_error_flag": (_i, [_p, _p]),
+    "qmm_variant_for": (ctypes.c_char_p, [_i, _i64, _i64, _i64, _i64, _i]),
+}
+
+_lib = None
+
+
+def lib_path():
+  return _build.LIB_PATH
+
+
+def lib():
+  """The loaded library; raises if it has not been built."""
+  global _lib
+  if _lib is None:
+    path = lib_path()
+    if not os.path.exists(path):
+      raise ImportError(
+          f"{path} is missing: build it with `python -m xla_b200._build` (needs nvcc). "
+          "xla_b200 has no CPU or PyTorch fallback for its kernels.")
+    L = ctypes.CDLL(path)
+    for name, (res, args) in SIGNATURES.items():
+      fn = getattr(L, name)
+      fn.restype, fn.argtypes = res, args
+    _lib = L
+  return _lib
+
+
+def dtype_code(dt):
+  try:
+    return _DTYPES[dt]
+  except KeyError:
+    raise TypeError(f"xla_b200: unsupported floating dtype {dt}") from None
+
+
+def ptr(t):
+  return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def stream_ptr(device=None):
+  return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def check(status):
+  """Turns a non-zero qmm_status into the Python exception the reference would raise."""
+  if status == 0:
+    return
+  L = lib()
+  msg = L.qmm_last_error_string().decode() or L.qmm_status_string(status).decode()
+  raise _STATUS_EXC.get(status, RuntimeError)(f"qmm_b200[{L.qmm_status_string(status).decode()}]: {msg}")
+
+
+def require_cuda(*tensors):
+  for t in tensors:
+    if t is not None and not t.is_cuda:
+      raise RuntimeError("xla_b200 kernels run on CUDA tensors only; there is no CPU path "
+                         f"(got a tensor on {t.device})")

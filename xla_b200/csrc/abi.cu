@@ -1,0 +1,431 @@
+// extern "C" entry points of libqmm_b200 (declared in include/qmm_b200.h): argument checks,
+// kernel-family selection, and the host-side helpers the kernels share.
+#include <cuda.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "ptx_sm100.cuh"
+
+namespace qmm {
+
+// ---- error reporting ----------------------------------------------------------------------
+static thread_local char g_last_error[512] = "";
+
+int fail(int status, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+  return status;
+}
+
+int check_launch(const char* what) {
+  cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) {
+    cudaGetLastError();  // clear the sticky-less launch error so later calls start clean
+    return fail(QMM_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+  }
+  return QMM_OK;
+}
+
+// ---- device queries -----------------------------------------------------------------------
+struct DeviceInfo {
+  bool known = false;
+  int sms = 0;
+  int cc_major = 0;
+};
+static DeviceInfo g_dev[64];
+
+static DeviceInfo* device_info() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  DeviceInfo* d = &g_dev[dev];
+  if (!d->known) {
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return nullptr;
+    d->sms = prop.multiProcessorCount;
+    d->cc_major = prop.major;
+    d->known = true;
+  }
+  return d;
+}
+
+int sm_count() {
+  DeviceInfo* d = device_info();
+  return d ? d->sms : 1;
+}
+
+bool device_is_sm100() {
+  DeviceInfo* d = device_info();
+  return d && d->cc_major == 10;
+}
+
+// One error word per device, living in the library's own device image.
+__device__ uint32_t g_qmm_error_word;
+
+uint32_t* device_error_word() {
+  static uint32_t* cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!cached[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_qmm_error_word) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    cached[dev] = reinterpret_cast<uint32_t*>(p);
+  }
+  return cached[dev];
+}
+
+// ---- tensor maps --------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+int encode_tmap_2d(CUtensorMap* map, const void* base, int elem_bytes, bool is_float16_family,
+                   uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(QMM_ERR_DEVICE, "driver does not provide cuTensorMapEncodeTiled");
+  CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  if (elem_bytes == 2) dt = is_float16_family ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
+  if (elem_bytes == 4) dt = CU_TENSOR_MAP_DATA_TYPE_UINT32;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * (uint64_t)elem_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(QMM_ERR_LAUNCH,
+                "cuTensorMapEncodeTiled failed (%d) for [%llu x %llu] elem %d box [%u x %u]", (int)r,
+                (unsigned long long)rows, (unsigned long long)cols, elem_bytes, box_rows, box_cols);
+  return QMM_OK;
+}
+
+// ---- argument checks ----------------------------------------------------------------------
+static int check_common(const void* x, int x_dt, const void* w, const float* scale, void* out,
+                        int out_dt, int64_t M, int64_t N, int64_t K) {
+  if (M < 0 || N < 0 || K < 0) return fail(QMM_ERR_BAD_SHAPE, "negative dimension (M=%lld N=%lld K=%lld)",
+                                           (long long)M, (long long)N, (long long)K);
+  if (!valid_float_dtype(x_dt) || !valid_float_dtype(out_dt))
+    return fail(QMM_ERR_UNSUPPORTED, "dtype must be QMM_F32, QMM_BF16 or QMM_F16 (x=%d out=%d)", x_dt, out_dt);
+  if (M * N == 0) return QMM_OK;
+  if (!out) return fail(QMM_ERR_NULL, "out is NULL");
+  if (K > 0 && (!x || !w)) return fail(QMM_ERR_NULL, "x or w is NULL");
+  if (!scale) return fail(QMM_ERR_NULL, "scale is NULL");
+  return QMM_OK;
+}
+
+static bool env_flag(const char* name) {
+  const char* v = getenv(name);
+  return v && v[0] && v[0] != '0';
+}
+
+static void log_choice(const char* op, const char* variant, int64_t M, int64_t N, int64_t K) {
+  static int on = -1;
+  if (on < 0) on = env_flag("QMM_B200_LOG") ? 1 : 0;
+  if (on) fprintf(stderr, "[qmm_b200] %s M=%lld N=%lld K=%lld -> %s\n", op, (long long)M, (long long)N,
+                  (long long)K, variant);
+}
+
+}  // namespace qmm
+
+using namespace qmm;
+
+extern "C" {
+
+int qmm_abi_version(void) { return QMM_ABI_VERSION; }
+
+const char* qmm_status_string(int status) {
+  switch (status) {
+    case QMM_OK: return "ok";
+    case QMM_ERR_BAD_SHAPE: return "bad shape";
+    case QMM_ERR_UNSUPPORTED: return "unsupported";
+    case QMM_ERR_MISALIGNED: return "misaligned";
+    case QMM_ERR_LAUNCH: return "launch failure";
+    case QMM_ERR_WORKSPACE: return "workspace too small";
+    case QMM_ERR_NULL: return "null pointer";
+    case QMM_ERR_DEVICE: return "device not supported";
+    case QMM_ERR_TIMEOUT: return "device-side wait timed out";
+    default: return "unknown status";
+  }
+}
+
+const char* qmm_last_error_string(void) { return g_last_error; }
+
+int qmm_w8a16_perchannel(const void* x, int x_dtype, const int8_t* w, const float* scale,
+                         const float* zp, void* out, int out_dtype, int64_t M, int64_t N,
+                         int64_t K, int variant, void* stream) {
+  int rc = check_common(x, x_dtype, w, scale, out, out_dtype, M, N, K);
+  if (rc != QMM_OK || M * N == 0) return rc;
+  cudaStream_t st = as_stream(stream);
+  if (variant == QMM_VARIANT_AUTO) {
+    if (mixed_tc_supported(8, M, N, K, 0, x, x_dtype, w, zp != nullptr) && M > 2)
+      variant = QMM_VARIANT_TCGEN05;
+    else if (gemv_nk_supported(8, M, N, K, 0, x, x_dtype, w))
+      variant = QMM_VARIANT_GEMV;
+    else if (mixed_tc_supported(8, M, N, K, 0, x, x_dtype, w, zp != nullptr))
+      variant = QMM_VARIANT_TCGEN05;
+    else
+      variant = QMM_VARIANT_GENERIC;
+  }
+  switch (variant) {
+    case QMM_VARIANT_GENERIC:
+      log_choice("w8a16_perchannel", "generic", M, N, K);
+      return launch_generic_nk(false, x, x_dtype, w, scale, zp, out, out_dtype, M, N, K, 0, st);
+    case QMM_VARIANT_GEMV:
+      log_choice("w8a16_perchannel", "gemv", M, N, K);
+      return launch_gemv_nk(8, x, x_dtype, w, scale, zp, out, out_dtype, M, N, K, 0, st);
+    case QMM_VARIANT_TCGEN05:
+      log_choice("w8a16_perchannel", "tcgen05", M, N, K);
+      if (zp) return fail(QMM_ERR_UNSUPPORTED, "tcgen05 weight-only kernel does not take a zero point");
+      return launch_mixed_tc(8, x, x_dtype, w, scale, out, out_dtype, M, N, K, 0, st);
+    default:
+      return fail(QMM_ERR_UNSUPPORTED, "unknown variant %d", variant);
+  }
+}
+
+int qmm_blockwise_sbn(const void* x, int x_dtype, const int8_t* w, const float* scale,
+                      const float* zp, void* out, int out_dtype, int64_t M, int64_t N, int64_t K,
+                      int64_t block_size, int variant, void* stream) {
+  int rc = check_common(x, x_dtype, w, scale, out, out_dtype, M, N, K);
+  if (rc != QMM_OK) return rc;
+  if (block_size <= 0 || K % block_size != 0)
+    return fail(QMM_ERR_BAD_SHAPE, "input_dim should be divisible by block_size, got input_dim: %lld, block_size: %lld",
+                (long long)K, (long long)block_size);
+  if (M * N == 0) return QMM_OK;
+  cudaStream_t st = as_stream(stream);
+  if (variant == QMM_VARIANT_AUTO)
+    variant = gemv_sbn_supported(M, N, K, block_size, w) ? QMM_VARIANT_GEMV : QMM_VARIANT_GENERIC;
+  switch (variant) {
+    case QMM_VARIANT_GENERIC:
+      log_choice("blockwise_sbn", "generic", M, N, K);
+      return launch_generic_sbn(x, x_dtype, w, scale, zp, out, out_dtype, M, N, K, block_size, st);
+    case QMM_VARIANT_GEMV:
+      log_choice("blockwise_sbn", "gemv", M, N, K);
+      return launch_gemv_sbn(x, x_dtype, w, scale, zp, out, out_dtype, M, N, K, block_size, st);
+    default:
+      return fail(QMM_ERR_UNSUPPORTED, "blockwise_sbn: variant %d is not available for this layout", variant);
+  }
+}
+
+int qmm_w4a16_blockwise_packed(const void* x, int x_dtype, const uint8_t* wp, const float* scale,
+                               const float* zp, void* out, int out_dtype, int64_t M, int64_t N,
+                               int64_t K, int64_t block_size, int variant, void* stream) {
+  int rc = check_common(x, x_dtype, wp, scale, out, out_dtype, M, N, K);
+  if (rc != QMM_OK) return rc;
+  if (K % 2 != 0) return fail(QMM_ERR_BAD_SHAPE, "packed int4 needs an even K, got %lld", (long long)K);
+  if (block_size <= 0 || K % block_size != 0)
+    return fail(QMM_ERR_BAD_SHAPE, "input_dim should be divisible by block_size, got input_dim: %lld, block_size: %lld",
+                (long long)K, (long long)block_size);
+  if (M * N == 0) return QMM_OK;
+  cudaStream_t st = as_stream(stream);
+  if (variant == QMM_VARIANT_AUTO) {
+    if (mixed_tc_supported(4, M, N, K, block_size, x, x_dtype, wp, zp != nullptr) && M > 1)
+      variant = QMM_VARIANT_TCGEN05;
+    else if (gemv_nk_supported(4, M, N, K, block_size, x, x_dtype, wp))
+      variant = QMM_VARIANT_GEMV;
+    else if (mixed_tc_supported(4, M, N, K, block_size, x, x_dtype, wp, zp != nullptr))
+      variant = QMM_VARIANT_TCGEN05;
+    else
+      variant = QMM_VARIANT_GENERIC;
+  }
+  switch (variant) {
+    case QMM_VARIANT_GENERIC:
+      log_choice("w4a16_blockwise_packed", "generic", M, N, K);
+      return launch_generic_nk(true, x, x_dtype, wp, scale, zp, out, out_dtype, M, N, K, block_size, st);
+    case QMM_VARIANT_GEMV:
+      log_choice("w4a16_blockwise_packed", "gemv", M, N, K);
+      return launch_gemv_nk(4, x, x_dtype, wp, scale, zp, out, out_dtype, M, N, K, block_size, st);
+    case QMM_VARIANT_TCGEN05:
+      log_choice("w4a16_blockwise_packed", "tcgen05", M, N, K);
+      if (zp) return fail(QMM_ERR_UNSUPPORTED, "tcgen05 weight-only kernel does not take a zero point");
+      return launch_mixed_tc(4, x, x_dtype, wp, scale, out, out_dtype, M, N, K, block_size, st);
+    default:
+      return fail(QMM_ERR_UNSUPPORTED, "unknown variant %d", variant);
+  }
+}
+
+int qmm_w4a16_perchannel_packed(const void* x, int x_dtype, const uint8_t* wp, const float* scale,
+                                const float* zp, void* out, int out_dtype, int64_t M, int64_t N,
+                                int64_t K, int variant, void* stream) {
+  int rc = check_common(x, x_dtype, wp, scale, out, out_dtype, M, N, K);
+  if (rc != QMM_OK) return rc;
+  if (K % 2 != 0) return fail(QMM_ERR_BAD_SHAPE, "packed int4 needs an even K, got %lld", (long long)K);
+  if (M * N == 0) return QMM_OK;
+  cudaStream_t st = as_stream(stream);
+  if (variant == QMM_VARIANT_AUTO) {
+    if (mixed_tc_supported(4, M, N, K, 0, x, x_dtype, wp, zp != nullptr) && M > 1)
+      variant = QMM_VARIANT_TCGEN05;
+    else if (gemv_nk_supported(4, M, N, K, 0, x, x_dtype, wp))
+      variant = QMM_VARIANT_GEMV;
+    else if (mixed_tc_supported(4, M, N, K, 0, x, x_dtype, wp, zp != nullptr))
+      variant = QMM_VARIANT_TCGEN05;
+    else
+      variant = QMM_VARIANT_GENERIC;
+  }
+  switch (variant) {
+    case QMM_VARIANT_GENERIC:
+      log_choice("w4a16_perchannel_packed", "generic", M, N, K);
+      return launch_generic_nk(true, x, x_dtype, wp, scale, zp, out, out_dtype, M, N, K, 0, st);
+    case QMM_VARIANT_GEMV:
+      log_choice("w4a16_perchannel_packed", "gemv", M, N, K);
+      return launch_gemv_nk(4, x, x_dtype, wp, scale, zp, out, out_dtype, M, N, K, 0, st);
+    case QMM_VARIANT_TCGEN05:
+      log_choice("w4a16_perchannel_packed", "tcgen05", M, N, K);
+      if (zp) return fail(QMM_ERR_UNSUPPORTED, "tcgen05 weight-only kernel does not take a zero point");
+      return launch_mixed_tc(4, x, x_dtype, wp, scale, out, out_dtype, M, N, K, 0, st);
+    default:
+      return fail(QMM_ERR_UNSUPPORTED, "unknown variant %d", variant);
+  }
+}
+
+int qmm_quantize_activation(const void* x, int x_dtype, int8_t* xq, float* x_scale,
+                            int32_t* xq_rowsum, int64_t M, int64_t K, int saturate, void* stream) {
+  if (M < 0 || K < 0) return fail(QMM_ERR_BAD_SHAPE, "negative dimension");
+  if (!valid_float_dtype(x_dtype)) return fail(QMM_ERR_UNSUPPORTED, "bad x dtype %d", x_dtype);
+  if (M == 0) return QMM_OK;
+  if (!x_scale || (K > 0 && (!x || !xq))) return fail(QMM_ERR_NULL, "x, xq or x_scale is NULL");
+  return launch_quantize_activation(x, x_dtype, xq, x_scale, xq_rowsum, M, K, saturate, as_stream(stream));
+}
+
+int qmm_w8a8_gemm(const int8_t* xq, const int8_t* w, const float* w_scale, const float* zp,
+                  const float* x_scale, const int32_t* xq_rowsum, int32_t* acc_out, void* out,
+                  int out_dtype, int64_t M, int64_t N, int64_t K, int variant, void* stream) {
+  if (M < 0 || N < 0 || K < 0) return fail(QMM_ERR_BAD_SHAPE, "negative dimension");
+  if (M * N == 0) return QMM_OK;
+  if (!acc_out && !out) return fail(QMM_ERR_NULL, "acc_out and out are both NULL");
+  if (out && !valid_float_dtype(out_dtype)) return fail(QMM_ERR_UNSUPPORTED, "bad out dtype %d", out_dtype);
+  if (out && (!w_scale || !x_scale)) return fail(QMM_ERR_NULL, "w_scale or x_scale is NULL");
+  if (zp && !xq_rowsum) return fail(QMM_ERR_NULL, "a zero point needs xq_rowsum");
+  if (K > 0 && (!xq || !w)) return fail(QMM_ERR_NULL, "xq or w is NULL");
+  cudaStream_t st = as_stream(stream);
+  if (variant == QMM_VARIANT_AUTO)
+    variant = (w8a8_tc_supported(M, N, K, xq, w) && M >= 16) ? QMM_VARIANT_TCGEN05 : QMM_VARIANT_GENERIC;
+  switch (variant) {
+    case QMM_VARIANT_GENERIC:
+      log_choice("w8a8_gemm", "generic", M, N, K);
+      return launch_generic_w8a8(xq, w, w_scale, zp, x_scale, xq_rowsum, acc_out, out, out_dtype, M, N, K, st);
+    case QMM_VARIANT_TCGEN05:
+      log_choice("w8a8_gemm", "tcgen05", M, N, K);
+      return launch_w8a8_tc(xq, w, w_scale, zp, x_scale, xq_rowsum, acc_out, out, out_dtype, M, N, K, st);
+    default:
+      return fail(QMM_ERR_UNSUPPORTED, "w8a8_gemm: variant %d is not available", variant);
+  }
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+size_t qmm_workspace_size(int op, int64_t M, int64_t N, int64_t K) {
+  (void)N;
+  if (op == QMM_OP_W8A8_PERCHANNEL) {
+    if (M <= 0 || K < 0) return 0;
+    // xq [M,K] int8 | x_scale [M] f32 | rowsum [M] i32, each 256-byte aligned
+    return align_up((size_t)M * (size_t)K, 256) + 2 * align_up((size_t)M * 4, 256);
+  }
+  return 0;
+}
+
+int qmm_w8a8_perchannel(const void* x, int x_dtype, const int8_t* w, const float* w_scale,
+                        const float* zp, void* out, int out_dtype, int64_t M, int64_t N,
+                        int64_t K, int saturate, int variant, void* workspace,
+                        size_t workspace_bytes, void* stream) {
+  int rc = check_common(x, x_dtype, w, w_scale, out, out_dtype, M, N, K);
+  if (rc != QMM_OK || M * N == 0) return rc;
+  const size_t need = qmm_workspace_size(QMM_OP_W8A8_PERCHANNEL, M, N, K);
+  if (!workspace || workspace_bytes < need)
+    return fail(QMM_ERR_WORKSPACE, "w8a8_perchannel needs %zu bytes of workspace, got %zu", need, workspace_bytes);
+  if (!aligned(workspace, 256)) return fail(QMM_ERR_MISALIGNED, "workspace must be 256-byte aligned");
+  uint8_t* base = reinterpret_cast<uint8_t*>(workspace);
+  int8_t* xq = reinterpret_cast<int8_t*>(base);
+  float* xs = reinterpret_cast<float*>(base + align_up((size_t)M * (size_t)K, 256));
+  int32_t* rowsum = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(xs) + align_up((size_t)M * 4, 256));
+  rc = qmm_quantize_activation(x, x_dtype, xq, xs, zp ? rowsum : nullptr, M, K, saturate, stream);
+  if (rc != QMM_OK) return rc;
+  return qmm_w8a8_gemm(xq, w, w_scale, zp, xs, zp ? rowsum : nullptr, nullptr, out, out_dtype, M, N, K,
+                       variant, stream);
+}
+
+int qmm_pack_int4_nk(const int8_t* w, uint8_t* wp, int64_t N, int64_t K, void* stream) {
+  if (N < 0 || K < 0 || K % 2 != 0) return fail(QMM_ERR_BAD_SHAPE, "pack_int4_nk: K must be even and sizes non-negative");
+  if (N * K == 0) return QMM_OK;
+  if (!w || !wp) return fail(QMM_ERR_NULL, "w or wp is NULL");
+  return launch_pack_int4_nk(w, wp, N, K, as_stream(stream));
+}
+
+int qmm_pack_int4_sbn(const int8_t* w, uint8_t* wp, int64_t S, int64_t block_size, int64_t N,
+                      void* stream) {
+  if (S < 0 || block_size < 0 || N < 0 || (S * block_size) % 2 != 0)
+    return fail(QMM_ERR_BAD_SHAPE, "pack_int4_sbn: K = S*block_size must be even and sizes non-negative");
+  if (S * block_size * N == 0) return QMM_OK;
+  if (!w || !wp) return fail(QMM_ERR_NULL, "w or wp is NULL");
+  return launch_pack_int4_sbn(w, wp, S, block_size, N, as_stream(stream));
+}
+
+int qmm_unpack_int4_nk(const uint8_t* wp, int8_t* w, int64_t N, int64_t K, void* stream) {
+  if (N < 0 || K < 0 || K % 2 != 0) return fail(QMM_ERR_BAD_SHAPE, "unpack_int4_nk: K must be even and sizes non-negative");
+  if (N * K == 0) return QMM_OK;
+  if (!w || !wp) return fail(QMM_ERR_NULL, "w or wp is NULL");
+  return launch_unpack_int4_nk(wp, w, N, K, as_stream(stream));
+}
+
+int qmm_device_error_flag(uint32_t* flag, void* stream) {
+  if (!flag) return fail(QMM_ERR_NULL, "flag is NULL");
+  uint32_t* word = device_error_word();
+  if (!word) return fail(QMM_ERR_DEVICE, "no CUDA device or error word unavailable");
+  cudaStream_t st = as_stream(stream);
+  cudaError_t e = cudaMemcpyAsync(flag, word, sizeof(uint32_t), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return fail(QMM_ERR_LAUNCH, "reading the device error word: %s", cudaGetErrorString(e));
+  if (*flag != 0) {
+    cudaMemsetAsync(word, 0, sizeof(uint32_t), st);
+    return fail(QMM_ERR_TIMEOUT, "a device-side wait gave up (code %u, CTA %u)", *flag & 0xff, *flag >> 8);
+  }
+  return QMM_OK;
+}
+
+const char* qmm_variant_for(int op, int64_t M, int64_t N, int64_t K, int64_t block_size, int has_zp) {
+  // Shape-only view of the AUTO heuristic (pointer alignment is assumed to be fine).
+  const void* ok = reinterpret_cast<const void*>(uintptr_t(256));
+  switch (op) {
+    case QMM_OP_W8A16_PERCHANNEL:
+      if (M > 2 && mixed_tc_supported(8, M, N, K, 0, ok, QMM_BF16, ok, has_zp != 0)) return "tcgen05";
+      if (gemv_nk_supported(8, M, N, K, 0, ok, QMM_BF16, ok)) return "gemv";
+      if (mixed_tc_supported(8, M, N, K, 0, ok, QMM_BF16, ok, has_zp != 0)) return "tcgen05";
+      return "generic";
+    case QMM_OP_W4A16_BLOCKWISE_PACKED:
+      if (M > 1 && mixed_tc_supported(4, M, N, K, block_size, ok, QMM_BF16, ok, has_zp != 0)) return "tcgen05";
+      if (gemv_nk_supported(4, M, N, K, block_size, ok, QMM_BF16, ok)) return "gemv";
+      if (mixed_tc_supported(4, M, N, K, block_size, ok, QMM_BF16, ok, has_zp != 0)) return "tcgen05";
+      return "generic";
+    case QMM_OP_BLOCKWISE_SBN:
+      return gemv_sbn_supported(M, N, K, block_size, ok) ? "gemv" : "generic";
+    case QMM_OP_W8A8_PERCHANNEL:
+      return (M >= 16 && K % 16 == 0 && K >= 16) ? "tcgen05" : "generic";
+    default:
+      return "generic";
+  }
+}
+
+}  // extern "C"

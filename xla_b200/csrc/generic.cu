@@ -1,0 +1,167 @@
+// Any-shape kernels: every semantic variant of the quantized linear, with no alignment or size
+// requirement.  They take the shapes the tensor-core and GEMV kernels refuse (odd K, tiny N,
+// zero points on large batches) so that the operator never needs a CPU fallback.
+//
+// Semantics follow torch_xla/experimental/xla_quantized_matmul.py:139-183.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace qmm {
+
+namespace {
+
+constexpr int kRowsPerWarp = 4;  // activation rows one warp carries per pass over a weight row
+constexpr int kWarps = 4;
+
+__device__ __forceinline__ int nibble_at(const uint8_t* wp, int64_t n, int64_t k, int64_t K) {
+  uint8_t b = wp[n * (K >> 1) + (k >> 1)];
+  int v = (k & 1) ? (b >> 4) : (b & 0xf);
+  return (v ^ 8) - 8;  // two's complement nibble
+}
+
+// Weights laid out [N,K] (int8) or [N,K/2] (packed int4).  One warp per output column n,
+// lanes stride over k, up to kRowsPerWarp activation rows per pass.
+// block_size == 0: per-channel (scale[n], zp[n]); else blockwise (scale[b*N+n], zp[b*N+n]).
+template <bool PACKED>
+__global__ void generic_nk_kernel(const void* __restrict__ x, int x_dt, const void* __restrict__ w,
+                                  const float* __restrict__ scale, const float* __restrict__ zp,
+                                  void* __restrict__ out, int out_dt, int64_t M, int64_t N,
+                                  int64_t K, int64_t block_size) {
+  const int lane = threadIdx.x & 31;
+  const int64_t n = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
+  const int64_t m0 = (int64_t)blockIdx.y * kRowsPerWarp;
+  if (n >= N) return;
+  float acc[kRowsPerWarp], corr[kRowsPerWarp];
+#pragma unroll
+  for (int j = 0; j < kRowsPerWarp; ++j) acc[j] = corr[j] = 0.f;
+
+  for (int64_t k = lane; k < K; k += 32) {
+    float wv;
+    if (PACKED)
+      wv = (float)nibble_at(reinterpret_cast<const uint8_t*>(w), n, k, K);
+    else
+      wv = (float)reinterpret_cast<const int8_t*>(w)[n * K + k];
+    float s = 1.f, z = 0.f;
+    if (block_size > 0) {
+      const int64_t b = k / block_size;
+      s = scale[b * N + n];
+      if (zp) z = zp[b * N + n];
+    } else if (zp) {
+      z = zp[n];
+    }
+#pragma unroll
+    for (int j = 0; j < kRowsPerWarp; ++j) {
+      if (m0 + j < M) {
+        const float xv = load_as_f32(x, (m0 + j) * K + k, x_dt);
+        acc[j] = fmaf(xv * wv, s, acc[j]);
+        corr[j] = fmaf(xv, z, corr[j]);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kRowsPerWarp; ++j) {
+    float a = warp_sum(acc[j]);
+    float c = warp_sum(corr[j]);
+    if (lane == 0 && m0 + j < M) {
+      const float v = (block_size > 0 ? a : a * scale[n]) - c;
+      store_from_f32(out, (m0 + j) * N + n, out_dt, v);
+    }
+  }
+}
+
+// Weights laid out [S, bs, N] (the reference's blockwise layout).  One thread per output
+// element, consecutive threads on consecutive n so that weight and scale reads coalesce.
+// Each block's dot product is finished before its scale is applied, as the reference does.
+__global__ void generic_sbn_kernel(const void* __restrict__ x, int x_dt,
+                                   const int8_t* __restrict__ w, const float* __restrict__ scale,
+                                   const float* __restrict__ zp, void* __restrict__ out, int out_dt,
+                                   int64_t M, int64_t N, int64_t K, int64_t block_size) {
+  const int64_t n = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t m = blockIdx.y;
+  if (n >= N || m >= M) return;
+  const int64_t S = K / block_size;
+  float total = 0.f;
+  for (int64_t b = 0; b < S; ++b) {
+    float part = 0.f, xs = 0.f;
+    for (int64_t c = 0; c < block_size; ++c) {
+      const int64_t k = b * block_size + c;
+      const float xv = load_as_f32(x, m * K + k, x_dt);
+      part = fmaf(xv, (float)w[k * N + n], part);
+      xs += xv;
+    }
+    total = fmaf(scale[b * N + n], part, total);
+    if (zp) total = fmaf(-xs, zp[b * N + n], total);
+  }
+  store_from_f32(out, m * N + n, out_dt, total);
+}
+
+// int8 x int8 -> int32, exact, with the fp32 epilogue in the reference's operation order.
+__global__ void generic_w8a8_kernel(const int8_t* __restrict__ xq, const int8_t* __restrict__ w,
+                                    const float* __restrict__ w_scale, const float* __restrict__ zp,
+                                    const float* __restrict__ x_scale,
+                                    const int32_t* __restrict__ rowsum, int32_t* __restrict__ acc_out,
+                                    void* __restrict__ out, int out_dt, int64_t M, int64_t N,
+                                    int64_t K) {
+  const int lane = threadIdx.x & 31;
+  const int64_t n = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
+  const int64_t m0 = (int64_t)blockIdx.y * kRowsPerWarp;
+  if (n >= N) return;
+  int32_t acc[kRowsPerWarp];
+#pragma unroll
+  for (int j = 0; j < kRowsPerWarp; ++j) acc[j] = 0;
+  for (int64_t k = lane; k < K; k += 32) {
+    const int32_t wv = w[n * K + k];
+#pragma unroll
+    for (int j = 0; j < kRowsPerWarp; ++j)
+      if (m0 + j < M) acc[j] += (int32_t)xq[(m0 + j) * K + k] * wv;
+  }
+#pragma unroll
+  for (int j = 0; j < kRowsPerWarp; ++j) {
+    int32_t a = acc[j];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+    if (lane == 0 && m0 + j < M) {
+      const int64_t m = m0 + j;
+      if (acc_out) acc_out[m * N + n] = a;
+      if (out) store_from_f32(out, m * N + n, out_dt, w8a8_dequant(a, w_scale[n], zp ? zp + n : nullptr,
+                                                                 rowsum ? rowsum[m] : 0, x_scale[m]));
+    }
+  }
+}
+
+}  // namespace
+
+int launch_generic_nk(bool packed, const void* x, int x_dt, const void* w, const float* scale,
+                      const float* zp, void* out, int out_dt, int64_t M, int64_t N, int64_t K,
+                      int64_t block_size, cudaStream_t st) {
+  dim3 grid((unsigned)ceil_div(N, kWarps), (unsigned)ceil_div(M, kRowsPerWarp));
+  if (grid.y > 65535) return fail(QMM_ERR_UNSUPPORTED, "generic kernel: M=%lld too large", (long long)M);
+  if (packed)
+    generic_nk_kernel<true><<<grid, kWarps * 32, 0, st>>>(x, x_dt, w, scale, zp, out, out_dt, M, N, K,
+                                                         block_size);
+  else
+    generic_nk_kernel<false><<<grid, kWarps * 32, 0, st>>>(x, x_dt, w, scale, zp, out, out_dt, M, N,
+                                                          K, block_size);
+  return check_launch("generic_nk_kernel");
+}
+
+int launch_generic_sbn(const void* x, int x_dt, const int8_t* w, const float* scale, const float* zp,
+                       void* out, int out_dt, int64_t M, int64_t N, int64_t K, int64_t block_size,
+                       cudaStream_t st) {
+  if (M > 65535) return fail(QMM_ERR_UNSUPPORTED, "generic kernel: M=%lld too large", (long long)M);
+  dim3 grid((unsigned)ceil_div(N, 128), (unsigned)M);
+  generic_sbn_kernel<<<grid, 128, 0, st>>>(x, x_dt, w, scale, zp, out, out_dt, M, N, K, block_size);
+  return check_launch("generic_sbn_kernel");
+}
+
+int launch_generic_w8a8(const int8_t* xq, const int8_t* w, const float* w_scale, const float* zp,
+                        const float* x_scale, const int32_t* rowsum, int32_t* acc_out, void* out,
+                        int out_dt, int64_t M, int64_t N, int64_t K, cudaStream_t st) {
+  dim3 grid((unsigned)ceil_div(N, kWarps), (unsigned)ceil_div(M, kRowsPerWarp));
+  if (grid.y > 65535) return fail(QMM_ERR_UNSUPPORTED, "generic kernel: M=%lld too large", (long long)M);
+  generic_w8a8_kernel<<<grid, kWarps * 32, 0, st>>>(xq, w, w_scale, zp, x_scale, rowsum, acc_out, out,
+                                                   out_dt, M, N, K);
+  return check_launch("generic_w8a8_kernel");
+}
+
+}  // namespace qmm

@@ -1,0 +1,69 @@
+// Internal launcher declarations shared by the translation units of libqmm_b200.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace qmm {
+
+// fp32 dequant of one W8A8 accumulator in the reference's operation order
+// (torch_xla/experimental/xla_quantized_matmul.py:159, 172-182): every product is rounded
+// separately, so the result matches the reference's fp32 output bit for bit.
+__device__ __forceinline__ float w8a8_dequant(int32_t acc, float w_scale, const float* zp_n,
+                                              int32_t rowsum, float x_scale) {
+  float v = __fmul_rn(__int2float_rn(acc), w_scale);
+  if (zp_n) v = __fsub_rn(v, __fmul_rn(__int2float_rn(rowsum), *zp_n));
+  return __fmul_rn(v, x_scale);
+}
+
+// ---- generic.cu ---------------------------------------------------------------------------
+int launch_generic_nk(bool packed, const void* x, int x_dt, const void* w, const float* scale,
+                      const float* zp, void* out, int out_dt, int64_t M, int64_t N, int64_t K,
+                      int64_t block_size, cudaStream_t st);
+int launch_generic_sbn(const void* x, int x_dt, const int8_t* w, const float* scale, const float* zp,
+                       void* out, int out_dt, int64_t M, int64_t N, int64_t K, int64_t block_size,
+                       cudaStream_t st);
+int launch_generic_w8a8(const int8_t* xq, const int8_t* w, const float* w_scale, const float* zp,
+                        const float* x_scale, const int32_t* rowsum, int32_t* acc_out, void* out,
+                        int out_dt, int64_t M, int64_t N, int64_t K, cudaStream_t st);
+
+// ---- gemv.cu ------------------------------------------------------------------------------
+// Decode kernels for weights stored [N,K] (int8) or [N,K/2] (packed int4).  block_size == 0
+// means per-channel scales.  Returns QMM_ERR_UNSUPPORTED / QMM_ERR_MISALIGNED when the shape
+// does not fit (M > 8, row pitch not a multiple of 16 bytes, ...).
+bool gemv_nk_supported(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size, const void* x,
+                       int x_dt, const void* w);
+int launch_gemv_nk(int wbits, const void* x, int x_dt, const void* w, const float* scale,
+                   const float* zp, void* out, int out_dt, int64_t M, int64_t N, int64_t K,
+                   int64_t block_size, cudaStream_t st);
+// Decode kernel for the reference's blockwise layout [S,bs,N].
+bool gemv_sbn_supported(int64_t M, int64_t N, int64_t K, int64_t block_size, const void* w);
+int launch_gemv_sbn(const void* x, int x_dt, const int8_t* w, const float* scale, const float* zp,
+                    void* out, int out_dt, int64_t M, int64_t N, int64_t K, int64_t block_size,
+                    cudaStream_t st);
+
+// ---- act_quant.cu -------------------------------------------------------------------------
+int launch_quantize_activation(const void* x, int x_dt, int8_t* xq, float* x_scale,
+                               int32_t* rowsum, int64_t M, int64_t K, int saturate,
+                               cudaStream_t st);
+
+// ---- pack.cu ------------------------------------------------------------------------------
+int launch_pack_int4_nk(const int8_t* w, uint8_t* wp, int64_t N, int64_t K, cudaStream_t st);
+int launch_pack_int4_sbn(const int8_t* w, uint8_t* wp, int64_t S, int64_t bs, int64_t N,
+                         cudaStream_t st);
+int launch_unpack_int4_nk(const uint8_t* wp, int8_t* w, int64_t N, int64_t K, cudaStream_t st);
+
+// ---- w8a8_gemm.cu (tcgen05 kind::i8) ------------------------------------------------------
+bool w8a8_tc_supported(int64_t M, int64_t N, int64_t K, const void* xq, const void* w);
+int launch_w8a8_tc(const int8_t* xq, const int8_t* w, const float* w_scale, const float* zp,
+                   const float* x_scale, const int32_t* rowsum, int32_t* acc_out, void* out,
+                   int out_dt, int64_t M, int64_t N, int64_t K, cudaStream_t st);
+
+// ---- mixed_gemm.cu (tcgen05 kind::f16 after shared-memory dequant) ------------------------
+bool mixed_tc_supported(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size, const void* x,
+                        int x_dt, const void* w, bool has_zp);
+int launch_mixed_tc(int wbits, const void* x, int x_dt, const void* w, const float* scale,
+                    void* out, int out_dt, int64_t M, int64_t N, int64_t K, int64_t block_size,
+                    cudaStream_t st);
+
+}  // namespace qmm

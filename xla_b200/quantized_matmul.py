@@ -1,0 +1,291 @@
+"""``torch.ops.xla.quantized_matmul`` and ``XlaQuantizedLinear`` on B200.
+
+Host-side mirror of torch_xla/experimental/xla_quantized_matmul.py: the same operator schema
+(:7-9), the same shape checks and messages (:12-53), the same module constructor, buffer names and
+``load_quantized_weight`` (:186-243).  The arithmetic runs in the sm_100a kernels behind the C ABI
+(include/qmm_b200.h); the kernel is registered for the CUDA dispatch key, plus a Meta kernel for
+tracing.  There is no CPU kernel here: CPU tensors fail in the dispatcher.
+
+Importing this module registers the ops, like importing the reference module does.
+"""
+import torch
+
+from . import _capi
+
+SCHEMA = ("quantized_matmul(Tensor x, Tensor w, Tensor scale, Tensor? zero_point=None, "
+          "int? block_size=-1, bool? int4_weight=False, bool? quantize_activation=False) -> Tensor")
+
+
+def has_xla_op(name):
+  try:
+    getattr(torch.ops.xla, name)
+    return True
+  except (AttributeError, RuntimeError):
+    return False
+
+
+# A FRAGMENT attaches to the ``xla`` namespace whether or not torch_xla created it first; the schema
+# is defined here only when nobody else has (torch_xla's own definition is byte-identical).
+XLA_LIB = torch.library.Library("xla", "FRAGMENT")
+if not has_xla_op("quantized_matmul"):
+  XLA_LIB.define(SCHEMA)
+
+# Kernel family forced for the calls made inside a `force_variant` block ("auto" otherwise).
+_variant = "auto"
+# How the activation quantizer converts a pre-cast +128: saturate to 127 (what an XLA device does)
+# or wrap to -128 (what the reference's eager CPU kernel does).
+_saturate = True
+
+
+class force_variant:
+  """Context manager: run the ops with one kernel family ("generic", "gemv", "tcgen05", "auto")."""
+
+  def __init__(self, name):
+    assert name in _capi.VARIANTS, name
+    self.name = name
+
+  def __enter__(self):
+    global _variant
+    self.prev, _variant = _variant, self.name
+
+  def __exit__(self, *exc):
+    global _variant
+    _variant = self.prev
+
+
+def set_activation_saturation(saturate: bool):
+  """True (default): int8 conversion clamps; False: wraps +128 to -128 like eager CPU."""
+  global _saturate
+  _saturate = bool(saturate)
+
+
+# ---- shape checks ---------------------------------------------------------------------------------
+# Conditions and AssertionError texts match the reference's validators (:12-53) so that code and
+# tests written against them see the same failures.
+
+
+def _expect(ok, message):
+  if not ok:
+    raise AssertionError(message)
+
+
+def _check_int8_rank(w, rank):
+  _expect(w.dtype == torch.int8, f"Weight dtype is expected to be torch.int8, got {w.dtype}.")
+  _expect(w.dim() == rank, f"Weight tensor is expected to be {rank}D, got {w.dim()}D Tensor.")
+
+
+def _check_per_channel_quant_weight_dtype_shapes(input_dim, output_dim, w, w_scaler, zero_point):
+  _check_int8_rank(w, 2)
+  dims = list(w.shape)
+  _expect(
+      dims == [output_dim, input_dim],
+      f"Weight shape is expected to be [output_dim, input_dim], output_dim: {output_dim}, "
+      f"input_dim: {input_dim}, but got {dims}.")
+  _expect(
+      w_scaler.dim() == 1 and w_scaler.shape[0] == dims[0],
+      f"weight scaler shape is expect to be [out_channel,], got {w_scaler.shape}, weight shape {dims}.")
+  if zero_point is not None:
+    _expect(
+        zero_point.dim() == 1 and w_scaler.shape[0] == dims[0],
+        f"zero point shape is expect to be [out_channel,], got {zero_point.shape}, weight shape {dims}.")
+
+
+def _check_blockwise_quant_weight_dtype_shapes(input_dim, output_dim, block_size, w, w_scaler,
+                                               zero_point):
+  _check_int8_rank(w, 3)
+  dims = list(w.shape)
+  _expect(
+      input_dim % block_size == 0, f"input_dim should be divisible by block_size, "
+      f"got input_dim: {input_dim}, block_size: {block_size}.")
+  _expect(
+      dims[0] == input_dim / block_size and dims[1] == block_size,
+      f"Weight shape is expected to be [input_dim / block_size, block_size, output_dim], "
+      f"input_dim: {input_dim}, block_size: {block_size}, output_dim: {output_dim}, "
+      f"but got {dims}.")
+  for name, t in (("weight scaler", w_scaler), ("zero_point", zero_point)):
+    if t is None:
+      continue
+    _expect(t.dim() == 2, f"{name} is expected to be 2D, got {t.dim()}D Tensor.")
+    _expect(
+        t.shape[0] == dims[0] and t.shape[1] == dims[-1],
+        f"{name} shape is expect to be [in_channel / block_size, out_channel], "
+        f"got {t.shape}, weight shape {dims}.")
+
+
+# ---- helpers ------------------------------------------------------------------------------------
+
+
+def _out_dtype(x, scaler, zero_point):
+  """The reference's output dtype is whatever type promotion of its eager ops gives (:158-182)."""
+  dt = torch.promote_types(x.dtype, scaler.dtype)
+  if zero_point is not None:
+    dt = torch.promote_types(dt, zero_point.dtype)
+  return dt
+
+
+def _f32(t):
+  if t is None:
+    return None
+  return t.contiguous() if t.dtype == torch.float32 else t.float().contiguous()
+
+
+def _rows(x):
+  """x as a contiguous [M, K] matrix."""
+  if x.dtype not in (torch.float32, torch.bfloat16, torch.float16):
+    raise TypeError(f"quantized_matmul: activation dtype {x.dtype} is not supported")
+  k = x.shape[-1]
+  x2 = x.reshape(-1, k)
+  return x2 if x2.is_contiguous() else x2.contiguous()
+
+
+def quantize_tensor(x, saturate=None):
+  """``_quantize_tensor`` of the reference (:56-73) as one kernel; returns (int8, scale in x.dtype)."""
+  _capi.require_cuda(x)
+  x2 = _rows(x)
+  M, K = x2.shape
+  xq = torch.empty((M, K), dtype=torch.int8, device=x.device)
+  xs = torch.empty((M,), dtype=torch.float32, device=x.device)
+  sat = _saturate if saturate is None else saturate
+  with torch.cuda.device(x.device):
+    _capi.check(_capi.lib().qmm_quantize_activation(
+        _capi.ptr(x2), _capi.dtype_code(x2.dtype), _capi.ptr(xq), _capi.ptr(xs), None, M, K, int(sat),
+        _capi.stream_ptr(x.device)))
+  return xq.reshape(x.shape), xs.to(x.dtype).reshape(x.shape[:-1] + (1,))
+
+
+def _w8a8(x2, w, scaler, zero_point, out_dtype):
+  L = _capi.lib()
+  M, K = x2.shape
+  N = w.shape[0]
+  out = torch.empty((M, N), dtype=out_dtype, device=x2.device)
+  if M * N == 0:
+    return out
+  nbytes = L.qmm_workspace_size(_capi.OP_W8A8_PERCHANNEL, M, N, K)
+  ws = torch.empty((nbytes,), dtype=torch.uint8, device=x2.device)
+  _capi.check(L.qmm_w8a8_perchannel(
+      _capi.ptr(x2), _capi.dtype_code(x2.dtype), _capi.ptr(w), _capi.ptr(scaler), _capi.ptr(zero_point),
+      _capi.ptr(out), _capi.dtype_code(out_dtype), M, N, K, int(_saturate), _capi.VARIANTS[_variant],
+      _capi.ptr(ws), nbytes, _capi.stream_ptr(x2.device)))
+  return out
+
+
+def quantized_matmul_cuda(x, w, scaler, zero_point=None, block_size=-1, int4_weight=False,
+                          quantize_activation=False):
+  """CUDA-key kernel of ``xla::quantized_matmul``; argument meaning as in the reference (:76-99)."""
+  block_size = -1 if block_size is None else block_size
+  quantize_activation = bool(quantize_activation)
+  _capi.require_cuda(x, w, scaler, zero_point)
+  K = x.shape[-1]
+  if block_size == -1:
+    _check_per_channel_quant_weight_dtype_shapes(K, scaler.shape[0], w, scaler, zero_point)
+    N = w.shape[0]
+  else:
+    assert quantize_activation == False, (  # noqa: E712 (kept as in the reference)
+        "Blockwise quantization does not support activation quantization.")
+    _check_blockwise_quant_weight_dtype_shapes(K, w.shape[-1], block_size, w, scaler, zero_point)
+    N = w.shape[-1]
+  out_dtype = _out_dtype(x, scaler, zero_point)
+  x2 = _rows(x)
+  M = x2.shape[0]
+  w = w if w.is_contiguous() else w.contiguous()
+  scaler32, zp32 = _f32(scaler), _f32(zero_point)
+  L = _capi.lib()
+  with torch.cuda.device(x.device):
+    if quantize_activation:
+      out = _w8a8(x2, w, scaler32, zp32, out_dtype)
+    else:
+      out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+      args = (_capi.ptr(x2), _capi.dtype_code(x2.dtype), _capi.ptr(w), _capi.ptr(scaler32), _capi.ptr(zp32),
+              _capi.ptr(out), _capi.dtype_code(out_dtype), M, N, K)
+      if block_size == -1:
+        _capi.check(L.qmm_w8a16_perchannel(*args, _capi.VARIANTS[_variant], _capi.stream_ptr(x.device)))
+      else:
+        _capi.check(L.qmm_blockwise_sbn(*args, block_size, _capi.VARIANTS[_variant],
+                                        _capi.stream_ptr(x.device)))
+  return out.reshape(x.shape[:-1] + (N,))
+
+
+def quantized_matmul_meta(x, w, scaler, zero_point=None, block_size=-1, int4_weight=False,
+                          quantize_activation=False):
+  """Shape/dtype-only kernel for fake tensors (torch.compile tracing)."""
+  block_size = -1 if block_size is None else block_size
+  n = w.shape[0] if block_size == -1 else w.shape[-1]
+  return torch.empty(x.shape[:-1] + (n,), dtype=_out_dtype(x, scaler, zero_point), device=x.device)
+
+
+XLA_LIB.impl("quantized_matmul", quantized_matmul_cuda, "CUDA")
+XLA_LIB.impl("quantized_matmul", quantized_matmul_meta, "Meta")
+
+
+class XlaQuantizedLinear(torch.nn.Module):
+  """Drop-in for the reference module (:186-243): same constructor, buffers and methods.
+
+  Buffers (and ``state_dict`` keys): ``weight`` int8, ``weight_scaler``, ``zero_point`` (only when
+  not symmetric).  Blockwise weights use the reference layout [in/block, block, out].
+
+  ``prepack=True`` additionally keeps a kernel-native copy of a blockwise weight (int4 packed two
+  per byte along K, built on first use on the GPU); the copy is derived state and is not saved.
+  """
+
+  def __init__(self, input_dim, output_dim, is_symmetric: bool = False, block_size: int = -1,
+               int4_weight: bool = False, quantize_activation: bool = False, prepack: bool = True):
+    super().__init__()
+    self.input_dim = input_dim
+    self.output_dim = output_dim
+    self.is_symmetric = is_symmetric
+    self.block_size = block_size
+    self.int4_weight = int4_weight
+    self.quantize_activation = quantize_activation
+    self.prepack = prepack
+    self._packed = None
+    self.register_buffer('weight', torch.zeros(output_dim, input_dim).to(torch.int8))
+    self.register_buffer('weight_scaler', torch.zeros(output_dim))
+    if not self.is_symmetric:
+      self.register_buffer('zero_point', torch.zeros(output_dim))
+    else:
+      self.zero_point = None
+
+  def load_quantized_weight(self, weight, weight_scaler, zero_point=None):
+    '''
+    weight (Tensor):
+      per-channel quant: [out_channel, in_channel].
+      block_wise quant: [in_channel / block_size, block_size, out_channel].
+
+    weight_scaler (Tensor):
+      per-channel quant: [out_channel,].
+      blockwise quant: [in_channel / block_size, out_channel].
+    '''
+    if self.block_size == -1:
+      _check_per_channel_quant_weight_dtype_shapes(self.input_dim, self.output_dim, weight,
+                                                   weight_scaler, zero_point)
+    else:
+      _check_blockwise_quant_weight_dtype_shapes(self.input_dim, self.output_dim, self.block_size,
+                                                 weight, weight_scaler, zero_point)
+    self.weight = weight
+    self.weight_scaler = weight_scaler
+    self.zero_point = zero_point
+    self._packed = None
+
+  def _packed_weight(self):
+    w = self.weight
+    key = (w.data_ptr(), w._version, w.device)
+    if self._packed is None or self._packed[0] != key:
+      from . import packed
+      self._packed = (key, packed.pack_int4(w, layout="sbn"))
+    return self._packed[1]
+
+  def forward(self, x):
+    if (self.prepack and self.block_size != -1 and self.int4_weight and self.weight.is_cuda and
+        self.weight.dim() == 3 and self.input_dim % 2 == 0):
+      from . import packed
+      return packed.quantized_matmul_packed(
+          x, self._packed_weight(), self.weight_scaler, self.zero_point, block_size=self.block_size,
+          int4_weight=True, weight_is_packed=True, out_dtype=_out_dtype(x, self.weight_scaler, self.zero_point))
+    return torch.ops.xla.quantized_matmul(
+        x,
+        self.weight,
+        self.weight_scaler,
+        self.zero_point,
+        block_size=self.block_size,
+        int4_weight=self.int4_weight,
+        quantize_activation=self.quantize_activation)
