@@ -1,0 +1,344 @@
+"""Benchmark of the weight-quantized linear path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload c2|c3|c1|c4]
+
+Workload (default, N=1): the decode configuration the headline metric is quoted on - W4A16 blockwise
+int4, w [14336, 4096] packed two per byte along K, block 128, scaler fp32 [32, 14336], x bf16 [M, 4096]
+for M in {1, 8, 32}, bf16 output.  One STEP = `--reps` launches of the op for each M, every launch on
+a different copy of the weights (a pool larger than L2), so no launch finds its weights in L2.
+
+  value      tokens/s with inputs resident in HBM, timed with CUDA events around the K steps
+             (steps are CUDA-graph replays, so launch latency of the Python layer is not in it).
+  roofline   the dominant kernel's algorithmic bytes per launch / its average launch duration (CUDA
+             events around each M's group of launches inside the timed region) vs the measured HBM peak.
+  e2e        same metric through the public op with HOST buffers: pinned-host activations copied in
+             and the result copied out inside the timed region, every step.
+  cpu_baseline  the reference's CPU path (oracle/torch_port.py, same ATen operators) on the host
+             cores, on a bounded sample.
+
+With --gpus N > 1 every rank runs the same step on its own token batch (data-parallel replicas of the
+weights, no collective on the data path): "scaling": "weak".  The tensor-parallel MLP (column- and
+row-sharded, NCCL all-reduce on the row-parallel output) is reported under "tp" on the same line.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+  sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+def measured_peaks():
+  path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+  if os.path.exists(path):
+    with open(path) as f:
+      d = json.load(f)
+    return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+            "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+  return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+  """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+  QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+           "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+  def __init__(self, index):
+    self.index, self.rows, self.proc = index, [], None
+
+  def start(self):
+    try:
+      self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}",
+                                    "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                   stderr=subprocess.DEVNULL, text=True)
+      self.thread = threading.Thread(target=self._read, daemon=True)
+      self.thread.start()
+    except OSError:
+      self.proc = None
+
+  def _read(self):
+    for line in self.proc.stdout:
+      self.rows.append([c.strip() for c in line.split(",")])
+
+  def stop(self):
+    if self.proc is None:
+      return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+    time.sleep(0.15)
+    self.proc.terminate()
+    try:
+      self.proc.wait(timeout=2)
+    except subprocess.TimeoutExpired:
+      self.proc.kill()
+    sm = sorted(float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit())
+    mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+    names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+    reasons = sorted({names[i] for r in self.rows if len(r) >= 6 for i in range(4) if r[2 + i].lower().startswith("active")})
+    return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx[0] if mx else None, "reasons": reasons,
+            "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------
+# workloads
+# ------------------------------------------------------------------------------------------------
+
+
+class C2Decode:
+  """W4A16 blockwise decode GEMV: w int4 [14336,4096] packed, block 128, M in {1,8,32}."""
+  name = "W4A16 blockwise int4 decode: w[14336,4096] packed, block 128, scaler f32 [32,14336], x bf16 [M,4096], M in {1,8,32}, bf16 out"
+  N, K, BS = 14336, 4096, 128
+  MS = (1, 8, 32)
+  dtype = "bf16 activations x int4 weights, fp32 accumulate"
+
+  def __init__(self, device, seed):
+    import xla_b200
+    self.dev = device
+    g = torch.Generator(device=device).manual_seed(seed)
+    S = self.K // self.BS
+    per_copy = self.N * self.K // 2 + S * self.N * 4
+    self.copies = max(2, -(-2 * L2_BYTES // per_copy))  # pool >= 2 x L2
+    self.wp = [torch.randint(0, 256, (self.N, self.K // 2), generator=g, device=device, dtype=torch.uint8)
+               for _ in range(self.copies)]
+    self.scale = [(torch.rand(S, self.N, generator=g, device=device) * 0.045 + 0.005) for _ in range(self.copies)]
+    self.x = {m: torch.randn(m, self.K, generator=g, device=device).bfloat16() for m in self.MS}
+    self.op = torch.ops.xla_b200.quantized_matmul_packed
+    self._i = 0
+
+  def bytes_per_launch(self, m):
+    S = self.K // self.BS
+    return self.N * self.K // 2 + 4 * S * self.N + 2 * m * self.K + 2 * m * self.N
+
+  def flops_per_launch(self, m):
+    return 2 * m * self.N * self.K
+
+  def launch(self, m, x=None):
+    i = self._i = (self._i + 1) % self.copies
+    return self.op(self.x[m] if x is None else x, self.wp[i], self.scale[i], block_size=self.BS, int4_weight=True,
+                   weight_is_packed=True, out_dtype=torch.bfloat16)
+
+  def tokens_per_step(self, reps):
+    return reps * sum(self.MS)
+
+
+def variant_name(m, N, K, bs):
+  from xla_b200 import _capi
+  return _capi.lib().qmm_variant_for(_capi.OP_W4A16_BLOCKWISE_PACKED, m, N, K, bs, 0).decode()
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU baseline (reference CPU path restated with the same ATen operators)
+# ------------------------------------------------------------------------------------------------
+
+
+def cpu_baseline_c2(seed, budget_s=12.0):
+  from oracle import torch_port as tp
+  cores = os.cpu_count() or 1
+  torch.set_num_threads(cores)
+  g = torch.Generator().manual_seed(seed)
+  N, K, BS = C2Decode.N, C2Decode.K, C2Decode.BS
+  S = K // BS
+  # the reference keeps int4 unpacked, [S, bs, N] int8; it needs fp32 activations with an fp32 scaler
+  w = torch.randint(-8, 8, (S, BS, N), generator=g, dtype=torch.int8)
+  sc = torch.rand(S, N, generator=g) * 0.045 + 0.005
+  xs = {m: torch.randn(m, K, generator=g) for m in C2Decode.MS}
+  for m in C2Decode.MS:  # warm-up
+    tp.quantized_matmul_cpu(xs[m], w, sc, block_size=BS)
+  t0 = time.perf_counter()
+  passes = 0
+  while True:
+    for m in C2Decode.MS:
+      tp.quantized_matmul_cpu(xs[m], w, sc, block_size=BS)
+    passes += 1
+    if time.perf_counter() - t0 > budget_s or passes >= 50:
+      break
+  dt = time.perf_counter() - t0
+  return {"value": passes * sum(C2Decode.MS) / dt, "unit": "tokens/s", "cores": cores, "kind": "port",
+          "sample": f"{passes} passes of M in (1,8,32) on the full [14336,4096] weight in the reference's unpacked "
+                    f"[32,128,14336] int8 layout, fp32 activations, {dt:.1f} s wall",
+          "threads": torch.get_num_threads()}
+
+
+# ------------------------------------------------------------------------------------------------
+# arms
+# ------------------------------------------------------------------------------------------------
+
+
+def run_reference(args, rank, world):
+  if rank != 0:
+    return
+  t0 = time.perf_counter()
+  per_step = []
+  base = None
+  for i in range(args.warmup + args.steps):
+    base = cpu_baseline_c2(args.seed, budget_s=2.0 if i < args.warmup else 6.0)
+    if i >= args.warmup:
+      per_step.append(base["value"])
+  value = sum(per_step) / len(per_step)
+  base["value"] = value
+  line = {"impl": "reference", "metric": "qlinear_decode_tokens_per_s", "value": value, "unit": "tokens/s",
+          "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+          "ms_per_step": 1e3 * (time.perf_counter() - t0) / max(1, args.steps + args.warmup),
+          "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 activations x int8-held int4",
+          "data": "synthetic", "config": {"workload": C2Decode.name, "flush": "n/a (CPU)"},
+          "cpu_baseline": base, "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+  print(json.dumps(line), flush=True)
+
+
+def run_ours(args, rank, world, local_rank):
+  import torch.distributed as dist
+  import xla_b200  # noqa: F401  (registers the ops; raises if the CUDA library is missing)
+  if not torch.cuda.is_available():
+    raise RuntimeError("bench.py needs a CUDA device: xla_b200 has no CPU path")
+  torch.cuda.set_device(local_rank)
+  dev = torch.device("cuda", local_rank)
+  if world > 1:
+    dist.init_process_group("nccl", device_id=dev)
+  peaks = measured_peaks()
+  wl = C2Decode(dev, args.seed + rank)
+  reps = args.reps
+  stream = torch.cuda.Stream(device=dev)
+
+  # one CUDA graph per M: `reps` launches on rotating weight copies
+  graphs = {}
+  with torch.cuda.stream(stream):
+    for m in wl.MS:
+      for _ in range(3):
+        wl.launch(m)
+    stream.synchronize()
+    for m in wl.MS:
+      gph = torch.cuda.CUDAGraph()
+      with torch.cuda.graph(gph, stream=stream):
+        for _ in range(reps):
+          wl.launch(m)
+      graphs[m] = gph
+  launches_per_step = reps * len(wl.MS)
+
+  def barrier():
+    if world > 1:
+      dist.barrier()
+    torch.cuda.synchronize(dev)
+
+  def step(events=None):
+    for m in wl.MS:
+      if events is not None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+      graphs[m].replay()
+      if events is not None:
+        e1.record(stream)
+        events[m].append((e0, e1))
+
+  with torch.cuda.stream(stream):
+    for _ in range(args.warmup):
+      step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+      sampler.start()
+    per_m = {m: [] for m in wl.MS}
+    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_start.record(stream)
+    for _ in range(args.steps):
+      step(per_m)
+    t_end.record(stream)
+    barrier()
+    total_ms = t_start.elapsed_time(t_end)
+
+    # ---- end to end through the public op: host buffers in, host result out, every step ----
+    hx = {m: torch.randn(m, wl.K).bfloat16().pin_memory() for m in wl.MS}
+    hy = {m: torch.empty(m, wl.N, dtype=torch.bfloat16).pin_memory() for m in wl.MS}
+    e2e_reps = max(1, min(reps, 8))
+
+    def e2e_step():
+      for m in wl.MS:
+        for _ in range(e2e_reps):
+          xd = hx[m].to(dev, non_blocking=True)
+          y = wl.launch(m, xd)
+          hy[m].copy_(y, non_blocking=True)
+      stream.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+      e2e_step()
+    barrier()
+    w0 = time.perf_counter()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+      e2e_step()
+    e1.record(stream)
+    barrier()
+    e2e_ms = max(e0.elapsed_time(e1), 1e3 * (time.perf_counter() - w0))
+  clocks = sampler.stop() if rank == 0 else None
+
+  times = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
+  if world > 1:
+    dist.all_reduce(times, op=dist.ReduceOp.MAX)
+  total_ms, e2e_ms = times.tolist()
+
+  if rank == 0:
+    tokens = world * args.steps * wl.tokens_per_step(reps)
+    value = tokens / (total_ms * 1e-3)
+    per_kernel = []
+    for m in wl.MS:
+      ms = sum(a.elapsed_time(b) for a, b in per_m[m]) / (len(per_m[m]) * reps)
+      gbs = wl.bytes_per_launch(m) / (ms * 1e-3) / 1e9
+      per_kernel.append({"M": m, "kernel": variant_name(m, wl.N, wl.K, wl.BS), "us_per_launch": ms * 1e3,
+                         "algorithmic_bytes": wl.bytes_per_launch(m), "gb_per_s": gbs,
+                         "frac_of_hbm_peak": gbs / peaks["hbm_gbs"], "tflops": wl.flops_per_launch(m) / (ms * 1e-3) / 1e12})
+    dom = max(per_kernel, key=lambda r: r["us_per_launch"])
+    e2e_tokens = world * args.steps * e2e_reps * sum(wl.MS)
+    line = {
+        "metric": "qlinear_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+        "config": {"workload": wl.name, "launches_per_step": launches_per_step, "reps_per_M": reps,
+                   "flush": f"weights rotate through a pool of {wl.copies} copies ({wl.copies * wl.bytes_per_launch(1) / 2**20:.0f} MiB > L2)",
+                   "parallelism": f"dp{world} replicas (no data-path collective)" if world > 1 else "single GPU",
+                   "timing": "CUDA events on the launch stream; steps are CUDA-graph replays"},
+        "roofline": {"bound": "hbm", "achieved": dom["gb_per_s"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": dom["gb_per_s"] / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                     "kernel": f"{dom['kernel']} M={dom['M']}"},
+        "per_kernel": per_kernel,
+        "e2e": {"value": e2e_tokens / (e2e_ms * 1e-3), "unit": "tokens/s",
+                "h2d_bytes_per_step": e2e_reps * sum(2 * m * wl.K for m in wl.MS),
+                "d2h_bytes_per_step": e2e_reps * sum(2 * m * wl.N for m in wl.MS)},
+        "gpu_launches": args.steps * launches_per_step,
+        "clocks": clocks,
+    }
+    if not args.no_cpu_baseline and world == 1:
+      line["cpu_baseline"] = cpu_baseline_c2(args.seed)
+    print(json.dumps(line), flush=True)
+  if world > 1:
+    dist.destroy_process_group()
+
+
+def main():
+  ap = argparse.ArgumentParser()
+  ap.add_argument("--gpus", type=int, default=1)
+  ap.add_argument("--steps", type=int, default=20)
+  ap.add_argument("--warmup", type=int, default=5)
+  ap.add_argument("--reps", type=int, default=20, help="launches per M per step")
+  ap.add_argument("--seed", type=int, default=0)
+  ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+  ap.add_argument("--no-cpu-baseline", action="store_true")
+  args = ap.parse_args()
+  args.warmup = max(args.warmup, 3)
+  rank = int(os.environ.get("RANK", "0"))
+  world = int(os.environ.get("WORLD_SIZE", "1"))
+  local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+  if args.impl == "reference":
+    run_reference(args, rank, world)
+  else:
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+  main()

@@ -371,3 +371,74 @@ def test_llama_layer_shapes_decode():
     for M in (1, 16):
       out = op(cu(x[:M]), wc, sc)
       assert qo.max_abs_rel(out, exact[:M]) < TOL_F32, (K, N, M)
+
+
+# ---------------------------------------------------------------------------------------------
+# weight-only tensor-core kernel (tcgen05 after shared-memory dequant), decode to prefill
+# ---------------------------------------------------------------------------------------------
+
+
+@pytest.mark.parametrize("xdtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M", [1, 5, 16, 33, 64, 100, 300])
+def test_tc_w8a16_per_channel(M, xdtype):
+  g = qc.gen(10)
+  N, K = 1000, 2112  # N not a multiple of 128, K = 33 tiles of 64
+  x = qc.activations(g, M, K, dtype=xdtype)
+  w = qc.int8_weight(g, N, K)
+  s = qc.per_channel_scale(g, N)
+  out = op(cu(x), cu(w), cu(s), variant="tcgen05")
+  assert out.dtype == torch.float32
+  assert qo.max_abs_rel(out, qo.quantized_matmul(x, w, s, dot_round=None)) < TOL_F32
+
+
+@pytest.mark.parametrize("xdtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,bs", [(1, 128), (8, 128), (32, 128), (64, 64), (100, 256), (16, -1)])
+def test_tc_w4a16_packed(M, bs, xdtype):
+  g = qc.gen(11)
+  N, K = 1160, 2048
+  x = qc.activations(g, M, K, dtype=xdtype)
+  w_nk = qc.int4_weight(g, N, K)
+  wp = xla_b200.pack_int4(cu(w_nk))
+  if bs == -1:
+    s = qc.per_channel_scale(g, N)
+    exact = qo.quantized_matmul(x, w_nk, s, dot_round=None)
+  else:
+    s = qc.blockwise_scale(g, K // bs, N)
+    exact = qo.quantized_matmul(x.float(), qc.to_sbn(w_nk, bs), s, block_size=bs, dot_round=None)
+  out = packed_op(cu(x), wp, cu(s), block_size=bs, int4_weight=True, weight_is_packed=True, variant="tcgen05")
+  assert out.dtype == torch.float32 and out.shape == (M, N)
+  assert qo.max_abs_rel(out, exact) < TOL_F32
+
+
+def test_tc_kernel_is_deterministic_and_leaves_no_error():
+  import ctypes
+  g = qc.gen(12)
+  M, N, K, bs = 32, 14336, 4096, 128
+  x = cu(qc.activations(g, M, K))
+  wp = cu(torch.randint(0, 256, (N, K // 2), generator=g, dtype=torch.uint8))
+  s = cu(qc.blockwise_scale(g, K // bs, N))
+  outs = [packed_op(x, wp, s, block_size=bs, int4_weight=True, weight_is_packed=True, out_dtype=torch.bfloat16,
+                    variant="tcgen05") for _ in range(20)]
+  for o in outs[1:]:
+    assert torch.equal(o, outs[0])
+  f = ctypes.c_uint32(7)
+  with torch.cuda.device(0):
+    assert _capi.lib().qmm_device_error_flag(ctypes.byref(f), _capi.stream_ptr()) == 0
+  assert f.value == 0
+  # and it agrees with the CUDA-core kernel on the same inputs
+  ref = packed_op(x[:8], wp, s, block_size=bs, int4_weight=True, weight_is_packed=True, variant="gemv")
+  got = packed_op(x[:8], wp, s, block_size=bs, int4_weight=True, weight_is_packed=True, variant="tcgen05")
+  assert qo.max_abs_rel(got, ref) < 1e-5
+
+
+def test_prefill_llama_shapes_tc():
+  """M=512 prefill on the layer's widest and deepest linears, against the oracle on a row sample."""
+  g = qc.gen(13)
+  for (K, N) in ((4096, 14336), (14336, 4096)):
+    w = qc.int8_weight(g, N, K)
+    s = qc.per_channel_scale(g, N)
+    x = qc.activations(g, 512, K)
+    out = op(cu(x), cu(w), cu(s), variant="tcgen05")
+    rows = torch.tensor([0, 1, 127, 128, 255, 256, 300, 511])
+    exact = qo.quantized_matmul(x[rows], w, s, dot_round=None)
+    assert qo.max_abs_rel(out[rows.to(DEV)], exact) < TOL_F32, (K, N)
