@@ -181,6 +181,14 @@ QMM_API int qmm_unpack_int4_nk(const uint8_t* wp, int8_t* w, int64_t N, int64_t 
  */
 QMM_API int qmm_device_error_flag(uint32_t* flag, void* stream);
 
+/*
+ * Pipeline tracing for the tensor-core weight-only kernel: while a device buffer of 4 x 1024 int64 is
+ * registered, CTA (0,0) of every launch logs SM-clock timestamps of its pipeline events into it
+ * (row 0 dequant warp, row 1 MMA issuer, row 2 drain warp, row 3 weight producer).  NULL turns it off.
+ * Stands in for the reference's TraceMe/xprof hooks on this path (torch_xla/debug/profiler.py:106-181).
+ */
+QMM_API int qmm_debug_set_trace(void* device_buffer);
+
 /* Name of the kernel family the AUTO heuristic picks (static string, for logs and tests). */
 QMM_API const char* qmm_variant_for(int op, int64_t M, int64_t N, int64_t K, int64_t block_size,
                             int has_zp);

@@ -38,6 +38,7 @@ SIGNATURES = {
     "qmm_pack_int4_sbn": (_i, [_p, _p, _i64, _i64, _i64, _p]),
     "qmm_unpack_int4_nk": (_i, [_p, _p, _i64, _i64, _p]),
     "qmm_device_error_flag": (_i, [_p, _p]),
+    "qmm_debug_set_trace": (_i, [_p]),
     "qmm_variant_for": (ctypes.c_char_p, [_i, _i64, _i64, _i64, _i64, _i]),
 }
 

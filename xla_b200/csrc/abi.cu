@@ -81,6 +81,9 @@ uint32_t* device_error_word() {
   return cached[dev];
 }
 
+static long long* g_trace = nullptr;
+long long* debug_trace_buffer() { return g_trace; }
+
 // ---- tensor maps --------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -402,6 +405,11 @@ int qmm_device_error_flag(uint32_t* flag, void* stream) {
     cudaMemsetAsync(word, 0, sizeof(uint32_t), st);
     return fail(QMM_ERR_TIMEOUT, "a device-side wait gave up (code %u, CTA %u)", *flag & 0xff, *flag >> 8);
   }
+  return QMM_OK;
+}
+
+int qmm_debug_set_trace(void* device_buffer) {
+  g_trace = reinterpret_cast<long long*>(device_buffer);
   return QMM_OK;
 }
 

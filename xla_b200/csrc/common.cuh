@@ -19,6 +19,9 @@ inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s
 // Word that kernels with bounded waits set when a wait gives up (0 = healthy).
 uint32_t* device_error_word();  // device address of the flag for the current device, or nullptr
 
+// Caller-provided device buffer for pipeline timestamps (nullptr = tracing off).
+long long* debug_trace_buffer();
+
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }

@@ -46,7 +46,14 @@ struct Params {
   int tiles_per_block;  // block_size / 64, or k_tiles for per-channel
   int blockwise;
   uint32_t* err_word;
+  long long* trace;  // optional pipeline timestamps of CTA (0,0), see qmm_debug_set_trace
 };
+
+// Per-role event log: role r writes clock64() stamps to trace[r * kTraceStride + i].
+constexpr int kTraceStride = 1024;
+__device__ __forceinline__ void stamp(const Params& p, int role, int& idx) {
+  if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && idx < kTraceStride) p.trace[role * kTraceStride + idx++] = clock64();
+}
 
 // Ring depths per token-tile width: decode tiles are HBM-bound and want a deep raw-weight ring; wide
 // prefill tiles are tensor-bound and spend the shared memory on activation tiles instead.
@@ -215,9 +222,11 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (warp == 0) {
     // ---------------- raw weight producer ----------------
     if (lane == 0) {
+      int ti = 0;
       for (int r = 0; r < n_raw; ++r) {
         const int s = r % kRawStages;
         ptx::mbar_wait(&raw_empty[s], ((r / kRawStages) & 1) ^ 1, abort_flag, p.err_word, ptx::kErrWaitEmpty);
+        stamp(p, 3, ti);
         ptx::mbar_expect_tx(&raw_full[s], kRawBytes);
         ptx::tma_load_2d(raw_base + (size_t)s * kRawBytes, &map_w, &raw_full[s], r * 128, (int32_t)n0);
       }
@@ -237,7 +246,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (lane == 0) {
       constexpr uint32_t fmt = kIsBf16 ? 1u : 0u;
       constexpr uint32_t idesc = ptx::make_idesc(/*f32*/ 1, fmt, fmt, BMW, MP);
-      int blk = 0, in_blk = 0;
+      int blk = 0, in_blk = 0, ti = 0;
       for (int t = 0; t < k_tiles; ++t) {
         const int buf = blk & 1;
         if (in_blk == 0) {
@@ -245,9 +254,13 @@ __global__ void __launch_bounds__(kThreads, 1)
           ptx::tcgen05_fence_after();
         }
         const int sa = t % kAStages, sb = t % kBStages;
+        stamp(p, 1, ti);
         ptx::mbar_wait(&a_full[sa], (t / kAStages) & 1, abort_flag, p.err_word, ptx::kErrWaitConv);
+        stamp(p, 1, ti);
         ptx::mbar_wait(&b_full[sb], (t / kBStages) & 1, abort_flag, p.err_word, ptx::kErrWaitFull);
+        stamp(p, 1, ti);
         ptx::tcgen05_fence_after();
+        stamp(p, 1, ti);
         const uint32_t a_addr = ptx::smem_u32(a_base + (size_t)sa * kABytes);
         const uint32_t b_addr = ptx::smem_u32(b_base + (size_t)sb * kBBytes);
         const uint32_t d_tmem = tmem_base + buf * MP;
@@ -255,9 +268,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int k = 0; k < BK / UMMA_K; ++k) {
           ptx::mma_f16_ss(d_tmem, ptx::make_sw128_kmajor_desc(a_addr + k * UMMA_K * 2),
                           ptx::make_sw128_kmajor_desc(b_addr + k * UMMA_K * 2), idesc, (in_blk | k) != 0 ? 1u : 0u);
+          stamp(p, 1, ti);
         }
         ptx::mma_commit(&a_empty[sa]);
+        stamp(p, 1, ti);
         ptx::mma_commit(&b_empty[sb]);
+        stamp(p, 1, ti);
         ++in_blk;
         if (in_blk == p.tiles_per_block || t == k_tiles - 1) {
           ptx::mma_commit(&acc_full[buf]);
@@ -271,15 +287,19 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int r = threadIdx.x - 128;
     const uint32_t sw = (uint32_t)(r & 7);
     int t = 0;  // operand tile counter
+    int ti = 0;
+    const bool tracer = (threadIdx.x == 128);
     for (int rs = 0; rs < n_raw; ++rs) {
       const int s = rs % kRawStages;
-      ptx::mbar_wait(&raw_full[s], (rs / kRawStages) & 1, abort_flag, p.err_word, ptx::kErrWaitRaw);
+      ptx::mbar_wait_warp(&raw_full[s], (rs / kRawStages) & 1, abort_flag, p.err_word, ptx::kErrWaitRaw);
       const uint32_t raw_row = ptx::smem_u32(raw_base + (size_t)s * kRawBytes) + r * 128;
 #pragma unroll
       for (int a = 0; a < TPR; ++a, ++t) {
         if (t >= k_tiles) break;
         const int sa = t % kAStages;
-        ptx::mbar_wait(&a_empty[sa], ((t / kAStages) & 1) ^ 1, abort_flag, p.err_word, ptx::kErrWaitEmpty);
+        if (tracer) stamp(p, 0, ti);
+        ptx::mbar_wait_warp(&a_empty[sa], ((t / kAStages) & 1) ^ 1, abort_flag, p.err_word, ptx::kErrWaitEmpty);
+        if (tracer) stamp(p, 0, ti);
         const uint32_t a_row = ptx::smem_u32(a_base + (size_t)sa * kABytes) + r * 128;
         if (WBITS == 4) {
           // two raw chunks (32 nibbles each) -> eight operand chunks (8 values each)
@@ -308,9 +328,11 @@ __global__ void __launch_bounds__(kThreads, 1)
             sts128(a_row + (((uint32_t)(jj * 2 + 1) ^ sw) << 4), q0, q1, q2, q3);
           }
         }
+        if (tracer) stamp(p, 0, ti);
         ptx::fence_proxy_async_smem();  // generic-proxy stores -> visible to the MMA's async proxy
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&a_full[sa]);
+        if (tracer) stamp(p, 0, ti);
       }
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&raw_empty[s]);
@@ -326,11 +348,15 @@ __global__ void __launch_bounds__(kThreads, 1)
       float acc[MP];
 #pragma unroll
       for (int j = 0; j < MP; ++j) acc[j] = 0.f;
+      int ti = 0;
+      const bool tracer = (threadIdx.x == 256);
       for (int b = 0; b < n_blocks; ++b) {
         const int buf = b & 1;
         const float s = n_ok ? __ldg(p.scale + (p.blockwise ? (int64_t)b * p.N + n : n)) : 0.f;
-        ptx::mbar_wait(&acc_full[buf], (b >> 1) & 1, abort_flag, p.err_word, ptx::kErrWaitTmemFull);
+        if (tracer) stamp(p, 2, ti);
+        ptx::mbar_wait_warp(&acc_full[buf], (b >> 1) & 1, abort_flag, p.err_word, ptx::kErrWaitTmemFull);
         ptx::tcgen05_fence_after();
+        if (tracer) stamp(p, 2, ti);
 #pragma unroll
         for (int c = 0; c < MP / 16; ++c) {
           uint32_t rr[16];
@@ -342,6 +368,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         ptx::tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
+        if (tracer) stamp(p, 2, ti);
       }
       if (n_ok) {
 #pragma unroll
@@ -351,7 +378,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     } else {
       // large token tiles: one scale block only (per-channel); scale and store straight from TMEM
       const float s = n_ok ? __ldg(p.scale + n) : 0.f;
-      ptx::mbar_wait(&acc_full[0], 0, abort_flag, p.err_word, ptx::kErrWaitTmemFull);
+      ptx::mbar_wait_warp(&acc_full[0], 0, abort_flag, p.err_word, ptx::kErrWaitTmemFull);
       ptx::tcgen05_fence_after();
 #pragma unroll 1
       for (int c = 0; c < MP / 32; ++c) {
@@ -452,6 +479,7 @@ int launch_mixed_tc(int wbits, const void* x, int x_dt, const void* w, const flo
   p.tiles_per_block = blockwise ? (int)(block_size / BK) : p.k_tiles;
   p.blockwise = blockwise ? 1 : 0;
   p.err_word = device_error_word();
+  p.trace = debug_trace_buffer();
   dim3 grid((unsigned)ceil_div(N, BMW), (unsigned)ceil_div(M, mp));
   if (grid.y > 65535) return fail(QMM_ERR_UNSUPPORTED, "weight-only tcgen05 kernel: M too large");
   if (wbits == 4) {

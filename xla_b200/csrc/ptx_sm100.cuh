@@ -2,7 +2,7 @@
 // mbarrier, TMA (cp.async.bulk.tensor), tcgen05.mma / TMEM, plus the shared-memory and
 // instruction descriptors tcgen05.mma consumes.
 //
-// Every wait is bounded: a wait that does not complete within kWaitLimitNs records a code in the
+// Every wait is bounded: a wait that does not complete within kWaitLimitCycles records a code in the
 // library's device error word and in a CTA-local abort flag; once that flag is set all later
 // waits return at once, so a kernel with a broken pipeline drains and exits instead of hanging.
 #pragma once
@@ -14,7 +14,7 @@
 namespace qmm {
 namespace ptx {
 
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
+constexpr long long kWaitLimitCycles = 4000000000ll;  // about 2 s of SM clock per wait
 
 enum ErrCode : uint32_t {
   kErrNone = 0,
@@ -82,17 +82,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // Bounded wait.  `abort_flag` is a CTA-shared word; `err_word` the library's global error word.
+// The fast path is a bare try_wait loop; the SM cycle counter is looked at only once every 4096
+// polls (a %globaltimer read per wait costs about a microsecond and would dominate short waits).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
                                           volatile uint32_t* abort_flag, uint32_t* err_word,
                                           uint32_t code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  if (*abort_flag) return false;
-  const unsigned long long t0 = globaltimer_ns();
   uint32_t spins = 0;
+  long long t0 = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 0x3ff) == 0) {
+    if ((++spins & 0xfff) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      const long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitLimitCycles) {
         *abort_flag = code;
         if (err_word) atomicCAS(err_word, 0u, code | (blockIdx.x << 8));
         return false;
@@ -100,6 +103,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
     }
   }
   return true;
+}
+
+// Whole-warp wait: lane 0 polls, the rest of the warp parks at the warp barrier.  Keeps 31 of 32
+// lanes from hammering the same mbarrier word while the single-thread MMA issuer needs that unit.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity,
+                                               volatile uint32_t* abort_flag, uint32_t* err_word,
+                                               uint32_t code) {
+  bool ok = true;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, err_word, code);
+  __syncwarp();
+  return ok;
 }
 
 // ---- proxies / fences ---------------------------------------------------------------------
