@@ -157,6 +157,27 @@ QMM_API int qmm_w8a8_perchannel(const void* x, int x_dtype, const int8_t* w, con
                         int64_t K, int saturate, int variant, void* workspace,
                         size_t workspace_bytes, void* stream);
 
+/*
+ * qmm_w8a8_perchannel for callers that cannot hand over device memory of their own: plugins inside
+ * a serving process whose framework owns every byte of the GPU, loops that must not hit
+ * cudaMalloc's device-wide synchronisation, code bound by a "no allocation after start-up" rule.
+ * (No counterpart in the reference: there the XLA runtime owns all temporaries.)
+ * The scratch between quantizer and contraction is a fixed array inside the library's device image,
+ * QMM_STATIC_SCRATCH_BYTES long, resident on every GPU that loads the library until the process ends.
+ *   - Shapes with qmm_workspace_size(QMM_OP_W8A8_PERCHANNEL, M, N, K) > QMM_STATIC_SCRATCH_BYTES are
+ *     refused with QMM_ERR_WORKSPACE (M*K up to 8 Mi elements fits, e.g. 2048 x 4096).
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *     that device current); make that first call before any stream capture starts.
+ *   - All calls share the one array and it keeps the previous call's contents; nothing in it needs
+ *     clearing, but two calls whose kernels may overlap on the GPU (other streams, other host
+ *     threads) corrupt each other: serialise them.
+ * The function itself calls no allocating routine.  Arguments as qmm_w8a8_perchannel.
+ */
+#define QMM_STATIC_SCRATCH_BYTES (8u * 1024u * 1024u + 64u * 1024u)
+QMM_API int qmm_w8a8_perchannel_static(const void* x, int x_dtype, const int8_t* w, const float* w_scale,
+                               const float* zp, void* out, int out_dtype, int64_t M, int64_t N,
+                               int64_t K, int saturate, int variant, void* stream);
+
 /* Bytes of caller-provided scratch an op needs for the given shape (0 if none). */
 QMM_API size_t qmm_workspace_size(int op, int64_t M, int64_t N, int64_t K);
 

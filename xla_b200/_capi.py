@@ -33,6 +33,7 @@ SIGNATURES = {
     "qmm_quantize_activation": (_i, [_p, _i, _p, _p, _p, _i64, _i64, _i, _p]),
     "qmm_w8a8_gemm": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i, _p]),
     "qmm_w8a8_perchannel": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i, _i, _p, _sz, _p]),
+    "qmm_w8a8_perchannel_static": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i, _i, _p]),
     "qmm_workspace_size": (_sz, [_i, _i64, _i64, _i64]),
     "qmm_pack_int4_nk": (_i, [_p, _p, _i64, _i64, _p]),
     "qmm_pack_int4_sbn": (_i, [_p, _p, _i64, _i64, _i64, _p]),
