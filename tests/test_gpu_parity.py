@@ -442,3 +442,41 @@ def test_prefill_llama_shapes_tc():
     rows = torch.tensor([0, 1, 127, 128, 255, 256, 300, 511])
     exact = qo.quantized_matmul(x[rows], w, s, dot_round=None)
     assert qo.max_abs_rel(out[rows.to(DEV)], exact) < TOL_F32, (K, N)
+
+
+# ---------------------------------------------------------------------------------------------
+# decode kernel with register dequant into warp-level MMAs (M <= 32)
+# ---------------------------------------------------------------------------------------------
+
+
+@pytest.mark.parametrize("xdtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,bs", [(1, 128), (7, 128), (8, 128), (9, 256), (16, 128), (17, 128), (32, 128), (4, -1), (24, -1)])
+def test_mma_w4a16_packed(M, bs, xdtype):
+  g = qc.gen(20)
+  N, K = 1000, 2304  # N not a multiple of 16; K = 18 steps of 128
+  x = qc.activations(g, M, K, dtype=xdtype)
+  w_nk = qc.int4_weight(g, N, K)
+  wp = xla_b200.pack_int4(cu(w_nk))
+  if bs == -1:
+    s = qc.per_channel_scale(g, N)
+    exact = qo.quantized_matmul(x, w_nk, s, dot_round=None)
+  else:
+    s = qc.blockwise_scale(g, K // bs, N)
+    exact = qo.quantized_matmul(x.float(), qc.to_sbn(w_nk, bs), s, block_size=bs, dot_round=None)
+  out = packed_op(cu(x), wp, cu(s), block_size=bs, int4_weight=True, weight_is_packed=True, variant="mma")
+  assert out.dtype == torch.float32 and out.shape == (M, N)
+  assert qo.max_abs_rel(out, exact) < TOL_F32
+
+
+@pytest.mark.parametrize("xdtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M", [1, 8, 13, 16, 32])
+def test_mma_w8a16_per_channel(M, xdtype):
+  g = qc.gen(21)
+  N, K = 1000, 2112  # 33 steps of 64
+  x = qc.activations(g, M, K, dtype=xdtype)
+  w = qc.int8_weight(g, N, K)
+  s = qc.per_channel_scale(g, N)
+  out = op(cu(x), cu(w), cu(s), variant="mma")
+  assert qo.max_abs_rel(out, qo.quantized_matmul(x, w, s, dot_round=None)) < TOL_F32
+  with pytest.raises(NotImplementedError):
+    op(cu(qc.activations(g, 33, K, dtype=xdtype)), cu(w), cu(s), variant="mma")

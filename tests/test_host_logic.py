@@ -100,7 +100,10 @@ def test_blockwise_rejects_activation_quantization_before_touching_the_gpu():
 
 def test_variant_heuristic_is_shape_only():
   L = xla_b200._capi.lib()
-  assert L.qmm_variant_for(xla_b200._capi.OP_W8A16_PERCHANNEL, 1, 4096, 4096, 0, 0) == b"gemv"
+  assert L.qmm_variant_for(xla_b200._capi.OP_W8A16_PERCHANNEL, 1, 4096, 4096, 0, 0) == b"mma"
+  assert L.qmm_variant_for(xla_b200._capi.OP_W8A16_PERCHANNEL, 1, 4096, 4096, 0, 1) == b"gemv"  # zero point
+  assert L.qmm_variant_for(xla_b200._capi.OP_W8A16_PERCHANNEL, 512, 4096, 4096, 0, 0) == b"tcgen05"
   assert L.qmm_variant_for(xla_b200._capi.OP_W8A16_PERCHANNEL, 3, 8, 5, 0, 0) == b"generic"
-  assert L.qmm_variant_for(xla_b200._capi.OP_W4A16_BLOCKWISE_PACKED, 1, 14336, 4096, 128, 0) == b"gemv"
+  assert L.qmm_variant_for(xla_b200._capi.OP_W4A16_BLOCKWISE_PACKED, 1, 14336, 4096, 128, 0) == b"mma"
+  assert L.qmm_variant_for(xla_b200._capi.OP_W4A16_BLOCKWISE_PACKED, 64, 14336, 4096, 128, 0) == b"tcgen05"
   assert L.qmm_variant_for(xla_b200._capi.OP_W8A8_PERCHANNEL, 2048, 4096, 4096, 0, 0) == b"tcgen05"

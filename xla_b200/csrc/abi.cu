@@ -177,22 +177,24 @@ const char* qmm_status_string(int status) {
 
 const char* qmm_last_error_string(void) { return g_last_error; }
 
+// AUTO choice for the weight-only ops on K-minor weights: the register-dequant MMA kernel for decode
+// batches, the tcgen05 kernel above that, the CUDA-core GEMV where those cannot go (zero points, f32
+// activations), the any-shape kernel for everything else.
+static int pick_weight_only(int wbits, int64_t M, int64_t N, int64_t K, int64_t bs, const void* x, int x_dt,
+                            const void* w, bool has_zp) {
+  if (decode_mma_supported(wbits, M, N, K, bs, x, x_dt, w, has_zp)) return QMM_VARIANT_MMA;
+  if (mixed_tc_supported(wbits, M, N, K, bs, x, x_dt, w, has_zp)) return QMM_VARIANT_TCGEN05;
+  if (gemv_nk_supported(wbits, M, N, K, bs, x, x_dt, w)) return QMM_VARIANT_GEMV;
+  return QMM_VARIANT_GENERIC;
+}
+
 int qmm_w8a16_perchannel(const void* x, int x_dtype, const int8_t* w, const float* scale,
                          const float* zp, void* out, int out_dtype, int64_t M, int64_t N,
                          int64_t K, int variant, void* stream) {
   int rc = check_common(x, x_dtype, w, scale, out, out_dtype, M, N, K);
   if (rc != QMM_OK || M * N == 0) return rc;
   cudaStream_t st = as_stream(stream);
-  if (variant == QMM_VARIANT_AUTO) {
-    if (mixed_tc_supported(8, M, N, K, 0, x, x_dtype, w, zp != nullptr) && M > 2)
-      variant = QMM_VARIANT_TCGEN05;
-    else if (gemv_nk_supported(8, M, N, K, 0, x, x_dtype, w))
-      variant = QMM_VARIANT_GEMV;
-    else if (mixed_tc_supported(8, M, N, K, 0, x, x_dtype, w, zp != nullptr))
-      variant = QMM_VARIANT_TCGEN05;
-    else
-      variant = QMM_VARIANT_GENERIC;
-  }
+  if (variant == QMM_VARIANT_AUTO) variant = pick_weight_only(8, M, N, K, 0, x, x_dtype, w, zp != nullptr);
   switch (variant) {
     case QMM_VARIANT_GENERIC:
       log_choice("w8a16_perchannel", "generic", M, N, K);
@@ -200,6 +202,10 @@ int qmm_w8a16_perchannel(const void* x, int x_dtype, const int8_t* w, const floa
     case QMM_VARIANT_GEMV:
       log_choice("w8a16_perchannel", "gemv", M, N, K);
       return launch_gemv_nk(8, x, x_dtype, w, scale, zp, out, out_dtype, M, N, K, 0, st);
+    case QMM_VARIANT_MMA:
+      log_choice("w8a16_perchannel", "mma", M, N, K);
+      if (zp) return fail(QMM_ERR_UNSUPPORTED, "the register-dequant decode kernel does not take a zero point");
+      return launch_decode_mma(8, x, x_dtype, w, scale, out, out_dtype, M, N, K, 0, st);
     case QMM_VARIANT_TCGEN05:
       log_choice("w8a16_perchannel", "tcgen05", M, N, K);
       if (zp) return fail(QMM_ERR_UNSUPPORTED, "tcgen05 weight-only kernel does not take a zero point");
@@ -244,16 +250,7 @@ int qmm_w4a16_blockwise_packed(const void* x, int x_dtype, const uint8_t* wp, co
                 (long long)K, (long long)block_size);
   if (M * N == 0) return QMM_OK;
   cudaStream_t st = as_stream(stream);
-  if (variant == QMM_VARIANT_AUTO) {
-    if (mixed_tc_supported(4, M, N, K, block_size, x, x_dtype, wp, zp != nullptr) && M > 1)
-      variant = QMM_VARIANT_TCGEN05;
-    else if (gemv_nk_supported(4, M, N, K, block_size, x, x_dtype, wp))
-      variant = QMM_VARIANT_GEMV;
-    else if (mixed_tc_supported(4, M, N, K, block_size, x, x_dtype, wp, zp != nullptr))
-      variant = QMM_VARIANT_TCGEN05;
-    else
-      variant = QMM_VARIANT_GENERIC;
-  }
+  if (variant == QMM_VARIANT_AUTO) variant = pick_weight_only(4, M, N, K, block_size, x, x_dtype, wp, zp != nullptr);
   switch (variant) {
     case QMM_VARIANT_GENERIC:
       log_choice("w4a16_blockwise_packed", "generic", M, N, K);
@@ -261,6 +258,10 @@ int qmm_w4a16_blockwise_packed(const void* x, int x_dtype, const uint8_t* wp, co
     case QMM_VARIANT_GEMV:
       log_choice("w4a16_blockwise_packed", "gemv", M, N, K);
       return launch_gemv_nk(4, x, x_dtype, wp, scale, zp, out, out_dtype, M, N, K, block_size, st);
+    case QMM_VARIANT_MMA:
+      log_choice("w4a16_blockwise_packed", "mma", M, N, K);
+      if (zp) return fail(QMM_ERR_UNSUPPORTED, "the register-dequant decode kernel does not take a zero point");
+      return launch_decode_mma(4, x, x_dtype, wp, scale, out, out_dtype, M, N, K, block_size, st);
     case QMM_VARIANT_TCGEN05:
       log_choice("w4a16_blockwise_packed", "tcgen05", M, N, K);
       if (zp) return fail(QMM_ERR_UNSUPPORTED, "tcgen05 weight-only kernel does not take a zero point");
@@ -278,16 +279,7 @@ int qmm_w4a16_perchannel_packed(const void* x, int x_dtype, const uint8_t* wp, c
   if (K % 2 != 0) return fail(QMM_ERR_BAD_SHAPE, "packed int4 needs an even K, got %lld", (long long)K);
   if (M * N == 0) return QMM_OK;
   cudaStream_t st = as_stream(stream);
-  if (variant == QMM_VARIANT_AUTO) {
-    if (mixed_tc_supported(4, M, N, K, 0, x, x_dtype, wp, zp != nullptr) && M > 1)
-      variant = QMM_VARIANT_TCGEN05;
-    else if (gemv_nk_supported(4, M, N, K, 0, x, x_dtype, wp))
-      variant = QMM_VARIANT_GEMV;
-    else if (mixed_tc_supported(4, M, N, K, 0, x, x_dtype, wp, zp != nullptr))
-      variant = QMM_VARIANT_TCGEN05;
-    else
-      variant = QMM_VARIANT_GENERIC;
-  }
+  if (variant == QMM_VARIANT_AUTO) variant = pick_weight_only(4, M, N, K, 0, x, x_dtype, wp, zp != nullptr);
   switch (variant) {
     case QMM_VARIANT_GENERIC:
       log_choice("w4a16_perchannel_packed", "generic", M, N, K);
@@ -295,6 +287,10 @@ int qmm_w4a16_perchannel_packed(const void* x, int x_dtype, const uint8_t* wp, c
     case QMM_VARIANT_GEMV:
       log_choice("w4a16_perchannel_packed", "gemv", M, N, K);
       return launch_gemv_nk(4, x, x_dtype, wp, scale, zp, out, out_dtype, M, N, K, 0, st);
+    case QMM_VARIANT_MMA:
+      log_choice("w4a16_perchannel_packed", "mma", M, N, K);
+      if (zp) return fail(QMM_ERR_UNSUPPORTED, "the register-dequant decode kernel does not take a zero point");
+      return launch_decode_mma(4, x, x_dtype, wp, scale, out, out_dtype, M, N, K, 0, st);
     case QMM_VARIANT_TCGEN05:
       log_choice("w4a16_perchannel_packed", "tcgen05", M, N, K);
       if (zp) return fail(QMM_ERR_UNSUPPORTED, "tcgen05 weight-only kernel does not take a zero point");
@@ -418,15 +414,15 @@ const char* qmm_variant_for(int op, int64_t M, int64_t N, int64_t K, int64_t blo
   const void* ok = reinterpret_cast<const void*>(uintptr_t(256));
   switch (op) {
     case QMM_OP_W8A16_PERCHANNEL:
-      if (M > 2 && mixed_tc_supported(8, M, N, K, 0, ok, QMM_BF16, ok, has_zp != 0)) return "tcgen05";
-      if (gemv_nk_supported(8, M, N, K, 0, ok, QMM_BF16, ok)) return "gemv";
-      if (mixed_tc_supported(8, M, N, K, 0, ok, QMM_BF16, ok, has_zp != 0)) return "tcgen05";
-      return "generic";
     case QMM_OP_W4A16_BLOCKWISE_PACKED:
-      if (M > 1 && mixed_tc_supported(4, M, N, K, block_size, ok, QMM_BF16, ok, has_zp != 0)) return "tcgen05";
-      if (gemv_nk_supported(4, M, N, K, block_size, ok, QMM_BF16, ok)) return "gemv";
-      if (mixed_tc_supported(4, M, N, K, block_size, ok, QMM_BF16, ok, has_zp != 0)) return "tcgen05";
+    case QMM_OP_W4A16_PERCHANNEL_PACKED: {
+      const int wbits = op == QMM_OP_W8A16_PERCHANNEL ? 8 : 4;
+      const int64_t bs = op == QMM_OP_W4A16_BLOCKWISE_PACKED ? block_size : 0;
+      if (decode_mma_supported(wbits, M, N, K, bs, ok, QMM_BF16, ok, has_zp != 0)) return "mma";
+      if (mixed_tc_shape_ok(wbits, M, N, K, bs, QMM_BF16, has_zp != 0)) return "tcgen05";
+      if (gemv_nk_supported(wbits, M, N, K, bs, ok, QMM_BF16, ok)) return "gemv";
       return "generic";
+    }
     case QMM_OP_BLOCKWISE_SBN:
       return gemv_sbn_supported(M, N, K, block_size, ok) ? "gemv" : "generic";
     case QMM_OP_W8A8_PERCHANNEL:

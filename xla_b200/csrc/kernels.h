@@ -42,6 +42,14 @@ int launch_gemv_sbn(const void* x, int x_dt, const int8_t* w, const float* scale
                     void* out, int out_dt, int64_t M, int64_t N, int64_t K, int64_t block_size,
                     cudaStream_t st);
 
+// ---- decode_mma.cu ------------------------------------------------------------------------
+// Decode kernel: weights dequantised in registers and fed to warp-level MMAs (M <= 32, bf16/f16
+// activations, no zero point).  block_size == 0 means per-channel scales.
+bool decode_mma_supported(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size, const void* x, int x_dt,
+                          const void* w, bool has_zp);
+int launch_decode_mma(int wbits, const void* x, int x_dt, const void* w, const float* scale, void* out, int out_dt,
+                      int64_t M, int64_t N, int64_t K, int64_t block_size, cudaStream_t st);
+
 // ---- act_quant.cu -------------------------------------------------------------------------
 int launch_quantize_activation(const void* x, int x_dt, int8_t* xq, float* x_scale,
                                int32_t* rowsum, int64_t M, int64_t K, int saturate,
@@ -60,6 +68,7 @@ int launch_w8a8_tc(const int8_t* xq, const int8_t* w, const float* w_scale, cons
                    int out_dt, int64_t M, int64_t N, int64_t K, cudaStream_t st);
 
 // ---- mixed_gemm.cu (tcgen05 kind::f16 after shared-memory dequant) ------------------------
+bool mixed_tc_shape_ok(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size, int x_dt, bool has_zp);
 bool mixed_tc_supported(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size, const void* x,
                         int x_dt, const void* w, bool has_zp);
 int launch_mixed_tc(int wbits, const void* x, int x_dt, const void* w, const float* scale,

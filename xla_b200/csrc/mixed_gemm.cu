@@ -436,15 +436,20 @@ int launch_mp(int mp, const CUtensorMap& map_w, const CUtensorMap& map_x, const 
 
 }  // namespace
 
-bool mixed_tc_supported(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size, const void* x,
-                        int x_dt, const void* w, bool has_zp) {
+bool mixed_tc_shape_ok(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size, int x_dt, bool has_zp) {
   if (has_zp) return false;
   if (x_dt != QMM_BF16 && x_dt != QMM_F16) return false;
   if (M < 1 || N < 1 || K < 64) return false;
   if ((K * wbits / 8) % 16 != 0 || (K * 2) % 16 != 0) return false;  // TMA row pitches
   if (block_size > 0 && (block_size % BK != 0 || K % block_size != 0)) return false;
-  if (!aligned(x, 16) || !aligned(w, 16)) return false;
   if (M > (1 << 20) || N > (1 << 28) || K > (1 << 28)) return false;
+  return true;
+}
+
+bool mixed_tc_supported(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size, const void* x,
+                        int x_dt, const void* w, bool has_zp) {
+  if (!mixed_tc_shape_ok(wbits, M, N, K, block_size, x_dt, has_zp)) return false;
+  if (!aligned(x, 16) || !aligned(w, 16)) return false;
   return device_is_sm100();
 }
 
