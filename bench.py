@@ -167,6 +167,172 @@ def cpu_baseline_c2(seed, budget_s=12.0):
 
 
 # ------------------------------------------------------------------------------------------------
+# the other benchmark configurations (reported beside the headline, N=1 only) and the TP MLP
+# ------------------------------------------------------------------------------------------------
+
+
+def time_graph(fn, stream, reps=10, iters=5, warm=2):
+  """us per call of fn(i): `reps` calls captured in one CUDA graph, replayed `iters` times."""
+  with torch.cuda.stream(stream):
+    for i in range(warm):
+      fn(i)
+    stream.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=stream):
+      for i in range(reps):
+        fn(i)
+    g.replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(iters):
+      g.replay()
+    e1.record(stream)
+    stream.synchronize()
+  return e0.elapsed_time(e1) * 1e3 / (iters * reps)
+
+
+def _rand_i8(gen, dev, n, k):
+  return torch.randint(-127, 128, (n, k), generator=gen, device=dev, dtype=torch.int8)
+
+
+def other_configs(dev, stream, peaks, seed):
+  """Per-configuration kernel timings: W8A16 decode (config 1), W8A8 prefill (config 3), the
+  Llama-3-8B-shaped layer (config 4) and the 70B-shaped MLP on one GPU (config 5)."""
+  import xla_b200
+  from xla_b200 import _capi
+  g = torch.Generator(device=dev).manual_seed(seed + 100)
+  qmm = torch.ops.xla.quantized_matmul
+  packed = torch.ops.xla_b200.quantized_matmul_packed
+  out = {}
+  hbm = peaks["hbm_gbs"]
+
+  # ---- config 1: W8A16 per-channel, x [16,4096], w [4096,4096] int8, module path ----
+  N = K = 4096
+  copies = 16
+  mods = []
+  for _ in range(copies):
+    m = xla_b200.XlaQuantizedLinear(K, N, is_symmetric=True)
+    m.load_quantized_weight(_rand_i8(g, dev, N, K), torch.rand(N, generator=g, device=dev) * 0.019 + 0.001)
+    mods.append(m)
+  x = torch.randn(16, K, generator=g, device=dev).bfloat16()
+  us = time_graph(lambda i: mods[i % copies](x), stream, reps=16)
+  byt = N * K + 4 * N + 2 * 16 * K + 4 * 16 * N
+  out["c1_w8a16_M16_4096x4096"] = {"us": us, "gb_per_s": byt / us / 1e3, "frac_of_hbm_peak": byt / us / 1e3 / hbm,
+                                   "kernel": _capi.lib().qmm_variant_for(_capi.OP_W8A16_PERCHANNEL, 16, N, K, 0, 0).decode(),
+                                   "out": "f32 (type promotion of bf16 x and f32 scaler)"}
+  del mods
+
+  # ---- config 3: W8A8, x [2048,4096] with 1% outliers x20, w [4096,4096] ----
+  M = 2048
+  xs = torch.randn(M, K, generator=g, device=dev)
+  xs = torch.where(torch.rand(M, K, generator=g, device=dev) < 0.01, xs * 20.0, xs).bfloat16()
+  ws = [_rand_i8(g, dev, N, K) for _ in range(8)]
+  sc = torch.rand(N, generator=g, device=dev) * 0.019 + 0.001
+  us_op = time_graph(lambda i: torch.ops.xla.quantized_matmul_int8(xs, ws[i % 8], sc, quantize_activation=True), stream,
+                     reps=8)
+  L = _capi.lib()
+  xq = torch.empty((M, K), dtype=torch.int8, device=dev)
+  xsc = torch.empty((M,), dtype=torch.float32, device=dev)
+  y = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+
+  def quant(i):
+    _capi.check(L.qmm_quantize_activation(_capi.ptr(xs), _capi.BF16, _capi.ptr(xq), _capi.ptr(xsc), None, M, K, 1,
+                                          _capi.stream_ptr(dev)))
+
+  def gemm(i):
+    _capi.check(L.qmm_w8a8_gemm(_capi.ptr(xq), _capi.ptr(ws[i % 8]), _capi.ptr(sc), None, _capi.ptr(xsc), None, None,
+                                _capi.ptr(y), _capi.BF16, M, N, K, _capi.TCGEN05, _capi.stream_ptr(dev)))
+
+  us_q = time_graph(quant, stream, reps=8)
+  us_g = time_graph(gemm, stream, reps=8)
+  ops = 2.0 * M * N * K
+  out["c3_w8a8_M2048_4096x4096"] = {
+      "us_op": us_op, "us_quantize": us_q, "us_gemm": us_g, "gemm_tops": ops / us_g / 1e6,
+      "gemm_frac_of_2x_bf16_burst_peak": ops / us_g / 1e6 / (2 * peaks["bf16_tflops"]),
+      "quantize_gb_per_s": 3.0 * M * K / us_q / 1e3, "op_tokens_per_s": M / (us_op * 1e-6),
+      "note": "int8 dense peak is not in MEASURED_PEAKS.json; fraction is against 2x the measured bf16 burst peak"}
+  del ws, xq, y
+
+  # ---- config 4: one Llama-3-8B-shaped layer, int8 per-channel, bf16 out, M in {1,16,64,512} ----
+  shapes = [(4096, 4096), (4096, 1024), (4096, 1024), (4096, 4096), (4096, 14336), (4096, 14336), (14336, 4096)]  # (K, N)
+  layers = []
+  for _ in range(2):  # two copies: 437 MB, so no weight is found in L2 again
+    layers.append([(_rand_i8(g, dev, n, k), (torch.rand(n, generator=g, device=dev) * 0.019 + 0.001).bfloat16())
+                   for (k, n) in shapes])
+  res4 = {}
+  for M in (1, 16, 64, 512):
+    xk = {k: torch.randn(M, k, generator=g, device=dev).bfloat16() for k in (4096, 14336)}
+
+    def layer(i):
+      for (w, s_) in layers[i % 2]:
+        qmm(xk[w.shape[1]], w, s_)  # bf16 scaler -> bf16 output
+
+    us = time_graph(layer, stream, reps=4, iters=3)
+    byt = sum(n * k + 4 * n + 2 * M * k + 2 * M * n for (k, n) in shapes)
+    fl = sum(2.0 * M * n * k for (k, n) in shapes)
+    res4[f"M{M}"] = {"us_per_layer": us, "layer_tokens_per_s": M / (us * 1e-6), "gb_per_s": byt / us / 1e3,
+                     "frac_of_hbm_peak": byt / us / 1e3 / hbm, "tflops": fl / us / 1e6,
+                     "kernel": _capi.lib().qmm_variant_for(_capi.OP_W8A16_PERCHANNEL, M, 4096, 4096, 0, 0).decode()}
+  out["c4_llama8b_layer_w8a16"] = res4
+  del layers
+
+  # ---- config 5 on one GPU: 70B-shaped MLP, W4A16 blockwise 128, M in {1,64,512} ----
+  out["c5_llama70b_mlp_w4a16_G1"] = tp_mlp_times(dev, stream, g, world=1, rank=0, peaks=peaks)
+  return out
+
+
+def tp_mlp_times(dev, stream, g, world, rank, peaks, Ms=(1, 64, 512)):
+  """gate/up [28672/G, 8192] column-sharded, down [8192, 28672/G] row-sharded + all-reduce (bf16)."""
+  import torch.distributed as dist
+  from xla_b200 import tensor_parallel as tp
+  H, F, BS = 8192, 28672, 128
+  fl_, hl = F // world, H
+  mk = lambda n, k: torch.randint(0, 256, (n, k // 2), generator=g, device=dev, dtype=torch.uint8)
+  mks = lambda k, n: torch.rand(k // BS, n, generator=g, device=dev) * 0.045 + 0.005
+  gate_w, up_w, down_w = mk(fl_, H), mk(fl_, H), mk(hl, fl_)
+  gate_s, up_s, down_s = mks(H, fl_), mks(H, fl_), mks(fl_, hl)
+  op = torch.ops.xla_b200.quantized_matmul_packed
+  res = {}
+  for M in Ms:
+    x = torch.randn(M, H, generator=g, device=dev).bfloat16()
+
+    def mlp(i):
+      a = op(x, gate_w, gate_s, block_size=BS, int4_weight=True, weight_is_packed=True, out_dtype=torch.bfloat16)
+      b = op(x, up_w, up_s, block_size=BS, int4_weight=True, weight_is_packed=True, out_dtype=torch.bfloat16)
+      del a  # gate*up is not part of the configuration: the three linears and the all-reduce are timed
+      y = op(b, down_w, down_s, block_size=BS, int4_weight=True, weight_is_packed=True, out_dtype=torch.bfloat16)
+      if world > 1:
+        dist.all_reduce(y)
+      return y
+
+    try:
+      us = time_graph(mlp, stream, reps=4, iters=3)
+      how = "cuda graph"
+    except Exception as e:  # graph capture of the collective refused: time eager launches instead
+      torch.cuda.synchronize(dev)
+      with torch.cuda.stream(stream):
+        for i in range(3):
+          mlp(i)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(10):
+          mlp(i)
+        e1.record(stream)
+        stream.synchronize()
+      us = e0.elapsed_time(e1) * 1e3 / 10
+      how = f"eager launches ({type(e).__name__} during capture)"
+    if world > 1:
+      t = torch.tensor([us], dtype=torch.float64, device=dev)
+      dist.all_reduce(t, op=dist.ReduceOp.MAX)
+      us = float(t.item())
+    byt = 3 * (fl_ * H // 2) + 4 * (2 * (H // BS) * fl_ + (fl_ // BS) * hl) + 2 * M * (2 * H + 3 * fl_ + hl)
+    res[f"M{M}"] = {"us_per_mlp": us, "tokens_per_s": M / (us * 1e-6), "gb_per_s_per_gpu": byt / us / 1e3,
+                    "frac_of_hbm_peak": byt / us / 1e3 / peaks["hbm_gbs"],
+                    "tflops_per_gpu": 3 * 2.0 * M * fl_ * H / us / 1e6, "timing": how}
+  return res
+
+
+# ------------------------------------------------------------------------------------------------
 # arms
 # ------------------------------------------------------------------------------------------------
 
@@ -277,6 +443,15 @@ def run_ours(args, rank, world, local_rank):
     barrier()
     e2e_ms = max(e0.elapsed_time(e1), 1e3 * (time.perf_counter() - w0))
   clocks = sampler.stop() if rank == 0 else None
+  extras = {}
+  if not args.headline_only:
+    g2 = torch.Generator(device=dev).manual_seed(args.seed + 7)
+    if world == 1:
+      extras["other_configs"] = other_configs(dev, stream, peaks, args.seed)
+    else:
+      extras["tp"] = {"config": "Llama-3-70B-shaped MLP, W4A16 block 128: gate/up [28672/G,8192] column-sharded, down "
+                                "[8192,28672/G] row-sharded, NCCL all-reduce of the bf16 output; scaling: strong",
+                      "G": world, "results": tp_mlp_times(dev, stream, g2, world, rank, peaks)}
 
   times = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
   if world > 1:
@@ -313,6 +488,7 @@ def run_ours(args, rank, world, local_rank):
         "gpu_launches": args.steps * launches_per_step,
         "clocks": clocks,
     }
+    line.update(extras)
     if not args.no_cpu_baseline and world == 1:
       line["cpu_baseline"] = cpu_baseline_c2(args.seed)
     print(json.dumps(line), flush=True)
@@ -329,6 +505,7 @@ def main():
   ap.add_argument("--seed", type=int, default=0)
   ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
   ap.add_argument("--no-cpu-baseline", action="store_true")
+  ap.add_argument("--headline-only", action="store_true", help="skip the other configurations / the TP MLP")
   args = ap.parse_args()
   args.warmup = max(args.warmup, 3)
   rank = int(os.environ.get("RANK", "0"))

@@ -8,17 +8,21 @@
 // torch_xla/csrc/xla_lower_util.cpp:477-481).
 //
 // "Swap-AB" orientation: the 128 weight rows of a CTA are the MMA M side, the token batch is the
-// MMA N side (16..256), so a decode batch of 1..16 tokens still fills a legal tcgen05 shape and the
-// kernel stays a pure weight stream.  Per CTA (12 warps):
-//   warp 0       TMA: raw weight bytes, 128 rows x 128 B per stage (128B swizzle)
-//   warp 1       MMA issuer (tcgen05.mma.kind::f16, M128 x N=MP x K16), owns the TMEM allocation
-//   warp 2       TMA: activation tiles [MP x 64] (zero-filled beyond M / K)
-//   warps 4..7   dequant: thread r converts row r of the raw stage to the activation dtype, exactly
-//                (integers up to 256 are exact in bf16 and fp16), and writes the 128B-swizzled
-//                K-major operand tile the MMA reads; no scale is applied here
-//   warps 8..11  drain: after each scale block, tcgen05.ld the block's partial sums and fold them into
-//                fp32 register accumulators with scale[b,n] - the reference's "dot per block, then
-//                scale, then sum", in fp32; two TMEM buffers overlap drain and MMA
+// MMA N side (16..256), so a small batch still fills a legal tcgen05 shape and the kernel stays a
+// weight stream.  Per CTA (16 warps):
+//   warp 0        TMA: raw weight bytes, 128 rows x 128 B per stage (128B swizzle)
+//   warp 1        MMA issuer (tcgen05.mma.kind::f16, M128 x N=MP x K16), owns the TMEM allocation
+//   warp 2        TMA: activation tiles [MP x 64] (zero-filled beyond M / K), several tiles per barrier
+//   warps 4..11   dequant: warp d converts operand tiles d, d+8, ... on its own (all 128 rows of a
+//                 64-wide k tile), exactly (integers up to 256 are exact in bf16 and fp16), into the
+//                 128B-swizzled K-major tile the MMA reads; eight tiles are in flight at once
+//   warps 12..15  drain: after each scale block, tcgen05.ld the block's partial sums and fold them into
+//                 fp32 register accumulators with scale[b,n] - the reference's "dot per block, then
+//                 scale, then sum", in fp32; two TMEM buffers overlap drain and MMA
+// Shapes with few weight rows (N/128 CTAs cannot fill 148 SMs) split K over a thread-block cluster:
+// the CTAs of a cluster take consecutive K ranges of the same 128 rows and the non-leaders add their
+// fp32 partials into the leader's shared memory (DSMEM) before the leader stores - deterministic,
+// no global scratch.
 #include <type_traits>
 
 #include "common.cuh"
@@ -32,10 +36,10 @@ namespace {
 constexpr int BMW = 128;          // weight rows per CTA (UMMA M)
 constexpr int BK = 64;            // k per operand tile (64 x 2 B = one 128-byte swizzle row)
 constexpr int UMMA_K = 16;
-constexpr int kAStages = 4;       // 16 KB each
+constexpr int kDequantWarps = 8;
 constexpr int kRawBytes = BMW * 128;
 constexpr int kABytes = BMW * BK * 2;
-constexpr int kThreads = 384;
+constexpr int kThreads = 512;
 
 struct Params {
   const float* scale;
@@ -44,29 +48,35 @@ struct Params {
   int64_t M, N, K;
   int k_tiles;          // ceil(K / 64)
   int tiles_per_block;  // block_size / 64, or k_tiles for per-channel
+  int tiles_per_cta;    // k tiles each CTA of a cluster takes (== k_tiles without split-K)
   int blockwise;
   uint32_t* err_word;
-  long long* trace;  // optional pipeline timestamps of CTA (0,0), see qmm_debug_set_trace
+  long long* trace;  // optional pipeline timestamps of CTA (0,0,0), see qmm_debug_set_trace
 };
 
 // Per-role event log: role r writes clock64() stamps to trace[r * kTraceStride + i].
 constexpr int kTraceStride = 1024;
 __device__ __forceinline__ void stamp(const Params& p, int role, int& idx) {
-  if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && idx < kTraceStride) p.trace[role * kTraceStride + idx++] = clock64();
+  if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && idx < kTraceStride)
+    p.trace[role * kTraceStride + idx++] = clock64();
 }
 
-// Ring depths per token-tile width: decode tiles are HBM-bound and want a deep raw-weight ring; wide
-// prefill tiles are tensor-bound and spend the shared memory on activation tiles instead.
+// Ring depths per token-tile width.  Decode-sized tiles are HBM-bound: deep raw-weight and operand
+// rings, activation tiles grouped four per barrier.  Prefill-sized tiles are tensor-bound and spend the
+// shared memory on activation tiles instead.
 template <int MP>
 struct Rings {
-  static constexpr int kRawStages = MP <= 64 ? 4 : (MP == 128 ? 3 : 2);  // 16 KB each
-  static constexpr int kBStages = MP <= 64 ? 8 : (MP == 128 ? 4 : 3);    // MP x 128 B each
+  static constexpr int kRawStages = MP <= 64 ? 4 : 2;                      // 16 KB each
+  static constexpr int kAStages = MP <= 32 ? 8 : (MP == 64 ? 6 : 4);       // 16 KB each
+  static constexpr int kBGroup = MP <= 32 ? 4 : (MP <= 128 ? 2 : 1);       // activation tiles per barrier
+  static constexpr int kBStages = MP <= 32 ? 2 : (MP == 64 ? 4 : (MP == 128 ? 2 : 3));  // groups in flight
+  static constexpr size_t kBytes = (size_t)kRawStages * kRawBytes + (size_t)kAStages * kABytes +
+                                   (size_t)kBStages * kBGroup * MP * 128;
 };
 
 template <int MP>
 constexpr size_t smem_bytes() {
-  return 1024 + (size_t)Rings<MP>::kRawStages * kRawBytes + (size_t)kAStages * kABytes +
-         (size_t)Rings<MP>::kBStages * MP * 128 + 512;
+  return 1024 + Rings<MP>::kBytes + 1024;
 }
 
 // ---- exact integer -> 16-bit float conversions, natural k order --------------------------------
@@ -153,8 +163,30 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, ui
   asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
-// WBITS 4|8; XT activation dtype (bf16|f16) = operand format of both MMA sides; MP = MMA N (tokens).
-template <int WBITS, typename XT, int MP>
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Address of the same shared-memory location in CTA `rank` of this cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+
+// WBITS 4|8; XT activation dtype (bf16|f16) = operand format of both MMA sides; MP = MMA N (tokens);
+// KSPLIT: the kernel is launched as clusters of gridDim.z CTAs along K (MP <= 64 only).
+template <int WBITS, typename XT, int MP, bool KSPLIT>
 __global__ void __launch_bounds__(kThreads, 1)
     mixed_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const Params p) {
@@ -163,6 +195,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   constexpr uint32_t kTmemCols = (2 * MP < 32) ? 32 : 2 * MP;
   constexpr bool kIsBf16 = !std::is_same<XT, __half>::value;
   constexpr int kRawStages = Rings<MP>::kRawStages;
+  constexpr int kAStages = Rings<MP>::kAStages;
+  constexpr int kBGroup = Rings<MP>::kBGroup;
   constexpr int kBStages = Rings<MP>::kBStages;
 
   extern __shared__ uint8_t smem_raw[];
@@ -170,10 +204,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint8_t* raw_base = smem;
   uint8_t* a_base = raw_base + (size_t)kRawStages * kRawBytes;
   uint8_t* b_base = a_base + (size_t)kAStages * kABytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(b_base + (size_t)kBStages * kBBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(b_base + (size_t)kBStages * kBGroup * kBBytes);
   uint64_t* raw_full = bars;                    // [kRawStages] TMA bytes
-  uint64_t* raw_empty = raw_full + kRawStages;  // [kRawStages] 4 dequant warps
-  uint64_t* a_full = raw_empty + kRawStages;    // [kAStages]   4 dequant warps
+  uint64_t* raw_empty = raw_full + kRawStages;  // [kRawStages] one arrival per tile of the stage
+  uint64_t* a_full = raw_empty + kRawStages;    // [kAStages]   the converting warp
   uint64_t* a_empty = a_full + kAStages;        // [kAStages]   tcgen05.commit
   uint64_t* b_full = a_empty + kAStages;        // [kBStages]   TMA bytes
   uint64_t* b_empty = b_full + kBStages;        // [kBStages]   tcgen05.commit
@@ -185,16 +219,21 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t n0 = (int64_t)blockIdx.x * BMW;
   const int64_t m0 = (int64_t)blockIdx.y * MP;
-  const int k_tiles = p.k_tiles;
-  const int n_raw = (k_tiles + TPR - 1) / TPR;
+  const uint32_t krank = KSPLIT ? cluster_ctarank() : 0u;
+  const int tile0 = (int)krank * p.tiles_per_cta;  // first k tile of this CTA
+  int my_tiles = p.k_tiles - tile0;
+  if (my_tiles > p.tiles_per_cta) my_tiles = p.tiles_per_cta;
+  if (my_tiles < 0) my_tiles = 0;
+  const int n_raw = (my_tiles + TPR - 1) / TPR;
+  const int n_groups = (my_tiles + kBGroup - 1) / kBGroup;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kRawStages; ++s) {
       ptx::mbar_init(&raw_full[s], 1);
-      ptx::mbar_init(&raw_empty[s], 4);
+      ptx::mbar_init(&raw_empty[s], TPR);
     }
     for (int s = 0; s < kAStages; ++s) {
-      ptx::mbar_init(&a_full[s], 4);
+      ptx::mbar_init(&a_full[s], 1);
       ptx::mbar_init(&a_empty[s], 1);
     }
     for (int s = 0; s < kBStages; ++s) {
@@ -223,22 +262,27 @@ __global__ void __launch_bounds__(kThreads, 1)
     // ---------------- raw weight producer ----------------
     if (lane == 0) {
       int ti = 0;
+      const int byte0 = tile0 * (BK * WBITS / 8);
       for (int r = 0; r < n_raw; ++r) {
         const int s = r % kRawStages;
         ptx::mbar_wait(&raw_empty[s], ((r / kRawStages) & 1) ^ 1, abort_flag, p.err_word, ptx::kErrWaitEmpty);
         stamp(p, 3, ti);
         ptx::mbar_expect_tx(&raw_full[s], kRawBytes);
-        ptx::tma_load_2d(raw_base + (size_t)s * kRawBytes, &map_w, &raw_full[s], r * 128, (int32_t)n0);
+        ptx::tma_load_2d(raw_base + (size_t)s * kRawBytes, &map_w, &raw_full[s], byte0 + r * 128, (int32_t)n0);
       }
     }
   } else if (warp == 2) {
-    // ---------------- activation tile producer ----------------
+    // ---------------- activation tile producer: kBGroup tiles per barrier ----------------
     if (lane == 0) {
-      for (int t = 0; t < k_tiles; ++t) {
-        const int s = t % kBStages;
-        ptx::mbar_wait(&b_empty[s], ((t / kBStages) & 1) ^ 1, abort_flag, p.err_word, ptx::kErrWaitEmpty);
-        ptx::mbar_expect_tx(&b_full[s], kBBytes);
-        ptx::tma_load_2d(b_base + (size_t)s * kBBytes, &map_x, &b_full[s], t * BK, (int32_t)m0);
+      for (int gidx = 0; gidx < n_groups; ++gidx) {
+        const int s = gidx % kBStages;
+        ptx::mbar_wait(&b_empty[s], ((gidx / kBStages) & 1) ^ 1, abort_flag, p.err_word, ptx::kErrWaitEmpty);
+        int cnt = my_tiles - gidx * kBGroup;
+        if (cnt > kBGroup) cnt = kBGroup;
+        ptx::mbar_expect_tx(&b_full[s], (uint32_t)cnt * kBBytes);
+        for (int j = 0; j < cnt; ++j)
+          ptx::tma_load_2d(b_base + ((size_t)s * kBGroup + j) * kBBytes, &map_x, &b_full[s],
+                           (tile0 + gidx * kBGroup + j) * BK, (int32_t)m0);
       }
     }
   } else if (warp == 1) {
@@ -246,61 +290,67 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (lane == 0) {
       constexpr uint32_t fmt = kIsBf16 ? 1u : 0u;
       constexpr uint32_t idesc = ptx::make_idesc(/*f32*/ 1, fmt, fmt, BMW, MP);
+      // descriptor halves: the high word is constant, the low word is the tile address >> 4
+      const uint32_t desc_hi = (uint32_t)(ptx::make_sw128_kmajor_desc(0) >> 32);
+      const uint32_t a_lo0 = (uint32_t)ptx::make_sw128_kmajor_desc(ptx::smem_u32(a_base));
+      const uint32_t b_lo0 = (uint32_t)ptx::make_sw128_kmajor_desc(ptx::smem_u32(b_base));
       int blk = 0, in_blk = 0, ti = 0;
-      for (int t = 0; t < k_tiles; ++t) {
+      for (int t = 0; t < my_tiles; ++t) {
         const int buf = blk & 1;
         if (in_blk == 0) {
           ptx::mbar_wait(&acc_empty[buf], ((blk >> 1) & 1) ^ 1, abort_flag, p.err_word, ptx::kErrWaitTmemEmpty);
-          ptx::tcgen05_fence_after();
         }
-        const int sa = t % kAStages, sb = t % kBStages;
+        const int sa = t % kAStages;
+        const int gb = t / kBGroup, sb = gb % kBStages, jb = t % kBGroup;
+        if (jb == 0) ptx::mbar_wait(&b_full[sb], (gb / kBStages) & 1, abort_flag, p.err_word, ptx::kErrWaitFull);
         stamp(p, 1, ti);
         ptx::mbar_wait(&a_full[sa], (t / kAStages) & 1, abort_flag, p.err_word, ptx::kErrWaitConv);
-        stamp(p, 1, ti);
-        ptx::mbar_wait(&b_full[sb], (t / kBStages) & 1, abort_flag, p.err_word, ptx::kErrWaitFull);
-        stamp(p, 1, ti);
         ptx::tcgen05_fence_after();
         stamp(p, 1, ti);
-        const uint32_t a_addr = ptx::smem_u32(a_base + (size_t)sa * kABytes);
-        const uint32_t b_addr = ptx::smem_u32(b_base + (size_t)sb * kBBytes);
+        const uint32_t a_lo = a_lo0 + (uint32_t)sa * (kABytes >> 4);
+        const uint32_t b_lo = b_lo0 + (uint32_t)(sb * kBGroup + jb) * (kBBytes >> 4);
         const uint32_t d_tmem = tmem_base + buf * MP;
 #pragma unroll
         for (int k = 0; k < BK / UMMA_K; ++k) {
-          ptx::mma_f16_ss(d_tmem, ptx::make_sw128_kmajor_desc(a_addr + k * UMMA_K * 2),
-                          ptx::make_sw128_kmajor_desc(b_addr + k * UMMA_K * 2), idesc, (in_blk | k) != 0 ? 1u : 0u);
-          stamp(p, 1, ti);
+          const uint64_t ad = ((uint64_t)desc_hi << 32) | (uint64_t)(a_lo + k * (UMMA_K * 2 >> 4));
+          const uint64_t bd = ((uint64_t)desc_hi << 32) | (uint64_t)(b_lo + k * (UMMA_K * 2 >> 4));
+          ptx::mma_f16_ss(d_tmem, ad, bd, idesc, (in_blk | k) != 0 ? 1u : 0u);
         }
         ptx::mma_commit(&a_empty[sa]);
-        stamp(p, 1, ti);
-        ptx::mma_commit(&b_empty[sb]);
-        stamp(p, 1, ti);
+        if (jb == kBGroup - 1 || t == my_tiles - 1) ptx::mma_commit(&b_empty[sb]);
         ++in_blk;
-        if (in_blk == p.tiles_per_block || t == k_tiles - 1) {
+        if (in_blk == p.tiles_per_block || t == my_tiles - 1) {
           ptx::mma_commit(&acc_full[buf]);
           in_blk = 0;
           ++blk;
         }
+        stamp(p, 1, ti);
       }
     }
-  } else if (warp >= 4 && warp < 8) {
-    // ---------------- dequant: thread r owns weight row r of the stage ----------------
-    const int r = threadIdx.x - 128;
-    const uint32_t sw = (uint32_t)(r & 7);
-    int t = 0;  // operand tile counter
+  } else if (warp >= 4 && warp < 4 + kDequantWarps) {
+    // ---------------- dequant: warp d owns operand tiles d, d+8, ...; lane owns rows lane+32i ----------------
+    // Each active warp owns ONE ring slot (slot == warp index), so a warp is never more than one
+    // barrier phase ahead of the slot it waits on: with fewer slots than warps, the surplus warps idle.
+    // (A warp two generations ahead of a slot would read the parity of an older phase as "done".)
+    constexpr int kActive = kAStages < kDequantWarps ? kAStages : kDequantWarps;
+    static_assert(kAStages % kActive == 0, "operand ring slots must map one-to-one onto converting warps");
+    const int dw = warp - 4;
     int ti = 0;
-    const bool tracer = (threadIdx.x == 128);
-    for (int rs = 0; rs < n_raw; ++rs) {
-      const int s = rs % kRawStages;
+    const bool tracer = (warp == 4 && lane == 0);
+    for (int t = dw; t < my_tiles && dw < kActive; t += kActive) {
+      const int rs = t / TPR, a = t % TPR;
+      const int s = rs % kRawStages, sa = t % kAStages;
+      if (tracer) stamp(p, 0, ti);
       ptx::mbar_wait_warp(&raw_full[s], (rs / kRawStages) & 1, abort_flag, p.err_word, ptx::kErrWaitRaw);
-      const uint32_t raw_row = ptx::smem_u32(raw_base + (size_t)s * kRawBytes) + r * 128;
+      ptx::mbar_wait_warp(&a_empty[sa], ((t / kAStages) & 1) ^ 1, abort_flag, p.err_word, ptx::kErrWaitEmpty);
+      if (tracer) stamp(p, 0, ti);
+      const uint32_t raw_tile = ptx::smem_u32(raw_base + (size_t)s * kRawBytes);
+      const uint32_t a_tile = ptx::smem_u32(a_base + (size_t)sa * kABytes);
 #pragma unroll
-      for (int a = 0; a < TPR; ++a, ++t) {
-        if (t >= k_tiles) break;
-        const int sa = t % kAStages;
-        if (tracer) stamp(p, 0, ti);
-        ptx::mbar_wait_warp(&a_empty[sa], ((t / kAStages) & 1) ^ 1, abort_flag, p.err_word, ptx::kErrWaitEmpty);
-        if (tracer) stamp(p, 0, ti);
-        const uint32_t a_row = ptx::smem_u32(a_base + (size_t)sa * kABytes) + r * 128;
+      for (int i = 0; i < 4; ++i) {
+        const int r = lane + 32 * i;
+        const uint32_t sw = (uint32_t)(r & 7);
+        const uint32_t raw_row = raw_tile + r * 128, a_row = a_tile + r * 128;
         if (WBITS == 4) {
           // two raw chunks (32 nibbles each) -> eight operand chunks (8 values each)
 #pragma unroll
@@ -328,31 +378,33 @@ __global__ void __launch_bounds__(kThreads, 1)
             sts128(a_row + (((uint32_t)(jj * 2 + 1) ^ sw) << 4), q0, q1, q2, q3);
           }
         }
-        if (tracer) stamp(p, 0, ti);
-        ptx::fence_proxy_async_smem();  // generic-proxy stores -> visible to the MMA's async proxy
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&a_full[sa]);
-        if (tracer) stamp(p, 0, ti);
       }
+      ptx::fence_proxy_async_smem();  // generic-proxy stores -> visible to the MMA's async proxy
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&raw_empty[s]);
+      if (lane == 0) {
+        ptx::mbar_arrive(&a_full[sa]);
+        ptx::mbar_arrive(&raw_empty[s]);
+      }
+      if (tracer) stamp(p, 0, ti);
     }
-  } else if (warp >= 8) {
+  } else if (warp >= 12) {
     // ---------------- drain / epilogue: thread owns output column n = n0 + its TMEM lane ----------------
     const int quad = warp & 3;
-    const int64_t n = n0 + quad * 32 + lane;
+    const int nl = quad * 32 + lane;
+    const int64_t n = n0 + nl;
     const bool n_ok = n < p.N;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-    const int n_blocks = (k_tiles + p.tiles_per_block - 1) / p.tiles_per_block;
+    const int n_blocks = (my_tiles + p.tiles_per_block - 1) / p.tiles_per_block;
+    const int block0 = tile0 / p.tiles_per_block;
     if constexpr (MP <= 64) {
       float acc[MP];
 #pragma unroll
       for (int j = 0; j < MP; ++j) acc[j] = 0.f;
       int ti = 0;
-      const bool tracer = (threadIdx.x == 256);
+      const bool tracer = (warp == 12 && lane == 0);
       for (int b = 0; b < n_blocks; ++b) {
         const int buf = b & 1;
-        const float s = n_ok ? __ldg(p.scale + (p.blockwise ? (int64_t)b * p.N + n : n)) : 0.f;
+        const float s = n_ok ? (p.blockwise ? __ldg(p.scale + (int64_t)(block0 + b) * p.N + n) : 1.f) : 0.f;
         if (tracer) stamp(p, 2, ti);
         ptx::mbar_wait_warp(&acc_full[buf], (b >> 1) & 1, abort_flag, p.err_word, ptx::kErrWaitTmemFull);
         ptx::tcgen05_fence_after();
@@ -370,31 +422,63 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
         if (tracer) stamp(p, 2, ti);
       }
-      if (n_ok) {
+      if constexpr (KSPLIT) {
+        // (1) every CTA of the cluster is past its main loop: the leader's rings may be overwritten
+        __syncwarp();
+        cluster_sync_all();
+        if (krank != 0) {
+          const uint32_t base = map_to_cta(ptx::smem_u32(smem), 0) + ((krank - 1) * MP * BMW + nl) * 4;
+#pragma unroll
+          for (int j = 0; j < MP; ++j) st_cluster_f32(base + j * BMW * 4, acc[j]);
+        }
+        // (2) partials have landed in the leader
+        __syncwarp();
+        cluster_sync_all();
+        if (krank == 0) {
+          const float* part = reinterpret_cast<const float*>(smem);
+          const int ks = (int)gridDim.z;
+          for (int z = 0; z < ks - 1; ++z)
+#pragma unroll
+            for (int j = 0; j < MP; ++j) acc[j] += part[(z * MP + j) * BMW + nl];
+        }
+      }
+      if (n_ok && krank == 0) {
+        const float ps = p.blockwise ? 1.f : __ldg(p.scale + n);
 #pragma unroll
         for (int j = 0; j < MP; ++j)
-          if (m0 + j < p.M) store_from_f32(p.out, (m0 + j) * p.N + n, p.out_dt, acc[j]);
+          if (m0 + j < p.M) store_from_f32(p.out, (m0 + j) * p.N + n, p.out_dt, acc[j] * ps);
       }
     } else {
       // large token tiles: one scale block only (per-channel); scale and store straight from TMEM
       const float s = n_ok ? __ldg(p.scale + n) : 0.f;
-      ptx::mbar_wait_warp(&acc_full[0], 0, abort_flag, p.err_word, ptx::kErrWaitTmemFull);
-      ptx::tcgen05_fence_after();
+      if (my_tiles > 0) {
+        ptx::mbar_wait_warp(&acc_full[0], 0, abort_flag, p.err_word, ptx::kErrWaitTmemFull);
+        ptx::tcgen05_fence_after();
 #pragma unroll 1
-      for (int c = 0; c < MP / 32; ++c) {
-        uint32_t rr[32];
-        __syncwarp();
-        ptx::tmem_ld_32x32b_x32(lane_addr + c * 32, rr);
-        ptx::tmem_ld_wait();
-        if (n_ok) {
+        for (int c = 0; c < MP / 32; ++c) {
+          uint32_t rr[32];
+          __syncwarp();
+          ptx::tmem_ld_32x32b_x32(lane_addr + c * 32, rr);
+          ptx::tmem_ld_wait();
+          if (n_ok) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int64_t m = m0 + c * 32 + j;
-            if (m < p.M) store_from_f32(p.out, m * p.N + n, p.out_dt, s * __uint_as_float(rr[j]));
+            for (int j = 0; j < 32; ++j) {
+              const int64_t m = m0 + c * 32 + j;
+              if (m < p.M) store_from_f32(p.out, m * p.N + n, p.out_dt, s * __uint_as_float(rr[j]));
+            }
           }
         }
+        ptx::tcgen05_fence_before();
       }
-      ptx::tcgen05_fence_before();
+    }
+  }
+  if constexpr (KSPLIT) {
+    // the warps that are not drain warps take part in the two cluster barriers as well
+    if (warp < 12) {
+      __syncwarp();
+      cluster_sync_all();
+      __syncwarp();
+      cluster_sync_all();
     }
   }
 
@@ -406,9 +490,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 }
 
-template <int WBITS, typename XT, int MP>
+template <int WBITS, typename XT, int MP, bool KSPLIT>
 int launch_one(const CUtensorMap& map_w, const CUtensorMap& map_x, const Params& p, dim3 grid, cudaStream_t st) {
-  auto kern = mixed_tc_kernel<WBITS, XT, MP>;
+  auto kern = mixed_tc_kernel<WBITS, XT, MP, KSPLIT>;
   constexpr size_t smem = smem_bytes<MP>();
   static bool attr_set[64] = {};
   int dev = 0;
@@ -418,19 +502,43 @@ int launch_one(const CUtensorMap& map_w, const CUtensorMap& map_x, const Params&
     if (e != cudaSuccess) return fail(QMM_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     if (dev >= 0 && dev < 64) attr_set[dev] = true;
   }
-  kern<<<grid, kThreads, smem, st>>>(map_w, map_x, p);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  if (KSPLIT) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = grid.z;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_w, map_x, p);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(QMM_ERR_LAUNCH, "mixed_tc_kernel launch: %s", cudaGetErrorString(e));
+  }
   return check_launch("mixed_tc_kernel");
 }
 
 template <int WBITS, typename XT>
-int launch_mp(int mp, const CUtensorMap& map_w, const CUtensorMap& map_x, const Params& p, dim3 grid,
+int launch_mp(int mp, bool ksplit, const CUtensorMap& map_w, const CUtensorMap& map_x, const Params& p, dim3 grid,
               cudaStream_t st) {
   switch (mp) {
-    case 16: return launch_one<WBITS, XT, 16>(map_w, map_x, p, grid, st);
-    case 32: return launch_one<WBITS, XT, 32>(map_w, map_x, p, grid, st);
-    case 64: return launch_one<WBITS, XT, 64>(map_w, map_x, p, grid, st);
-    case 128: return launch_one<WBITS, XT, 128>(map_w, map_x, p, grid, st);
-    default: return launch_one<WBITS, XT, 256>(map_w, map_x, p, grid, st);
+    case 16:
+      return ksplit ? launch_one<WBITS, XT, 16, true>(map_w, map_x, p, grid, st)
+                    : launch_one<WBITS, XT, 16, false>(map_w, map_x, p, grid, st);
+    case 32:
+      return ksplit ? launch_one<WBITS, XT, 32, true>(map_w, map_x, p, grid, st)
+                    : launch_one<WBITS, XT, 32, false>(map_w, map_x, p, grid, st);
+    case 64:
+      return ksplit ? launch_one<WBITS, XT, 64, true>(map_w, map_x, p, grid, st)
+                    : launch_one<WBITS, XT, 64, false>(map_w, map_x, p, grid, st);
+    case 128: return launch_one<WBITS, XT, 128, false>(map_w, map_x, p, grid, st);
+    default: return launch_one<WBITS, XT, 256, false>(map_w, map_x, p, grid, st);
   }
 }
 
@@ -485,14 +593,29 @@ int launch_mixed_tc(int wbits, const void* x, int x_dt, const void* w, const flo
   p.blockwise = blockwise ? 1 : 0;
   p.err_word = device_error_word();
   p.trace = debug_trace_buffer();
-  dim3 grid((unsigned)ceil_div(N, BMW), (unsigned)ceil_div(M, mp));
-  if (grid.y > 65535) return fail(QMM_ERR_UNSUPPORTED, "weight-only tcgen05 kernel: M too large");
-  if (wbits == 4) {
-    if (x_dt == QMM_BF16) return launch_mp<4, __nv_bfloat16>(mp, map_w, map_x, p, grid, st);
-    return launch_mp<4, __half>(mp, map_w, map_x, p, grid, st);
+  const int64_t n_tiles = ceil_div(N, BMW), m_tiles = ceil_div(M, mp);
+  if (m_tiles > 65535) return fail(QMM_ERR_UNSUPPORTED, "weight-only tcgen05 kernel: M too large");
+  // split K over a cluster when the (n, m) tiles alone leave most SMs idle; the leader needs room for
+  // (ks-1) fp32 partial tiles of 128 x mp in the shared memory its rings used
+  int ks = 1;
+  if (mp <= 64) {
+    const int64_t ctas = n_tiles * m_tiles;
+    const int room = 1 + (int)((160 * 1024) / (mp * BMW * 4));
+    while (ks < 8 && ks * 2 <= room && ctas * ks * 2 <= (int64_t)sm_count() &&
+           p.k_tiles / (ks * 2) >= 4 * (blockwise ? p.tiles_per_block : 1))
+      ks *= 2;
   }
-  if (x_dt == QMM_BF16) return launch_mp<8, __nv_bfloat16>(mp, map_w, map_x, p, grid, st);
-  return launch_mp<8, __half>(mp, map_w, map_x, p, grid, st);
+  const int unit = blockwise ? p.tiles_per_block : 1;  // a CTA's K range holds whole scale blocks
+  p.tiles_per_cta = (int)(ceil_div(ceil_div(p.k_tiles, ks), unit) * unit);
+  if (!blockwise && ks > 1) p.tiles_per_block = p.tiles_per_cta;  // per-channel: one block per CTA
+  if (!blockwise && ks == 1) p.tiles_per_cta = p.k_tiles;
+  dim3 grid((unsigned)n_tiles, (unsigned)m_tiles, (unsigned)ks);
+  if (wbits == 4) {
+    if (x_dt == QMM_BF16) return launch_mp<4, __nv_bfloat16>(mp, ks > 1, map_w, map_x, p, grid, st);
+    return launch_mp<4, __half>(mp, ks > 1, map_w, map_x, p, grid, st);
+  }
+  if (x_dt == QMM_BF16) return launch_mp<8, __nv_bfloat16>(mp, ks > 1, map_w, map_x, p, grid, st);
+  return launch_mp<8, __half>(mp, ks > 1, map_w, map_x, p, grid, st);
 }
 
 }  // namespace qmm
