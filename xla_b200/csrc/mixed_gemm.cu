@@ -13,9 +13,10 @@
 //   warp 0        TMA: raw weight bytes, 128 rows x 128 B per stage (128B swizzle)
 //   warp 1        MMA issuer (tcgen05.mma.kind::f16, M128 x N=MP x K16), owns the TMEM allocation
 //   warp 2        TMA: activation tiles [MP x 64] (zero-filled beyond M / K), several tiles per barrier
-//   warps 4..11   dequant: warp d converts operand tiles d, d+8, ... on its own (all 128 rows of a
+//   warps 4,6,7,8,10,11  dequant: each converts whole operand tiles on its own (all 128 rows of a
 //                 64-wide k tile), exactly (integers up to 256 are exact in bf16 and fp16), into the
-//                 128B-swizzled K-major tile the MMA reads; eight tiles are in flight at once
+//                 128B-swizzled K-major tile the MMA reads; six tiles are in flight at once.  They avoid
+//                 the scheduler partition of the MMA issuer (warps 5 and 9 stay idle)
 //   warps 12..15  drain: after each scale block, tcgen05.ld the block's partial sums and fold them into
 //                 fp32 register accumulators with scale[b,n] - the reference's "dot per block, then
 //                 scale, then sum", in fp32; two TMEM buffers overlap drain and MMA
@@ -36,7 +37,7 @@ namespace {
 constexpr int BMW = 128;          // weight rows per CTA (UMMA M)
 constexpr int BK = 64;            // k per operand tile (64 x 2 B = one 128-byte swizzle row)
 constexpr int UMMA_K = 16;
-constexpr int kDequantWarps = 8;
+constexpr int kDequantWarps = 6;
 constexpr int kRawBytes = BMW * 128;
 constexpr int kABytes = BMW * BK * 2;
 constexpr int kThreads = 512;
@@ -61,22 +62,31 @@ __device__ __forceinline__ void stamp(const Params& p, int role, int& idx) {
     p.trace[role * kTraceStride + idx++] = clock64();
 }
 
-// Ring depths per token-tile width.  Decode-sized tiles are HBM-bound: deep raw-weight and operand
-// rings, activation tiles grouped four per barrier.  Prefill-sized tiles are tensor-bound and spend the
-// shared memory on activation tiles instead.
-template <int MP>
+// Ring depths per weight width and token-tile width.  Decode-sized tiles are HBM-bound: deep raw-weight
+// and operand rings, activation tiles grouped per barrier.  Prefill-sized tiles are tensor-bound and spend
+// the shared memory on activation tiles instead.
+//
+// mbarrier waits only tell "the phase with this parity is over", so a waiter must never be two phases
+// ahead of a barrier.  The rings make that structural: every converting warp owns one operand slot
+// (kAStages == converting warps), and a warp waits for its operand slot before its raw stage.
+template <int WBITS, int MP>
 struct Rings {
-  static constexpr int kRawStages = MP <= 64 ? 4 : 2;                      // 16 KB each
-  static constexpr int kAStages = MP <= 32 ? 8 : (MP == 64 ? 6 : 4);       // 16 KB each
-  static constexpr int kBGroup = MP <= 32 ? 4 : (MP <= 128 ? 2 : 1);       // activation tiles per barrier
-  static constexpr int kBStages = MP <= 32 ? 2 : (MP == 64 ? 4 : (MP == 128 ? 2 : 3));  // groups in flight
+  static constexpr int kTilesPerRaw = (WBITS == 4) ? 4 : 2;
+  static constexpr int kAStages = kDequantWarps;                          // 16 KB each, one per converting warp
+  static constexpr int kRawStages = 4;                                    // 16 KB each
+  static constexpr int kBGroup = MP <= 32 ? 4 : (MP <= 128 ? 2 : 1);      // activation tiles per barrier
+  static constexpr int kBStages = MP == 64 ? 4 : 2;                       // groups in flight
+  // the converting warp waits for its operand slot first (tile t-kAStages consumed, hence every raw
+  // stage up to that tile has landed); that covers the previous generation of its raw slot if
+  static_assert(kRawStages * kTilesPerRaw - kTilesPerRaw + 1 >= kAStages, "raw ring generation vs operand ring");
   static constexpr size_t kBytes = (size_t)kRawStages * kRawBytes + (size_t)kAStages * kABytes +
                                    (size_t)kBStages * kBGroup * MP * 128;
+  static_assert(kBytes + 2048 <= 227 * 1024, "shared memory budget");
 };
 
-template <int MP>
+template <int WBITS, int MP>
 constexpr size_t smem_bytes() {
-  return 1024 + Rings<MP>::kBytes + 1024;
+  return 1024 + Rings<WBITS, MP>::kBytes + 1024;
 }
 
 // ---- exact integer -> 16-bit float conversions, natural k order --------------------------------
@@ -194,10 +204,11 @@ __global__ void __launch_bounds__(kThreads, 1)
   constexpr uint32_t kBBytes = MP * 128;
   constexpr uint32_t kTmemCols = (2 * MP < 32) ? 32 : 2 * MP;
   constexpr bool kIsBf16 = !std::is_same<XT, __half>::value;
-  constexpr int kRawStages = Rings<MP>::kRawStages;
-  constexpr int kAStages = Rings<MP>::kAStages;
-  constexpr int kBGroup = Rings<MP>::kBGroup;
-  constexpr int kBStages = Rings<MP>::kBStages;
+  using R = Rings<WBITS, MP>;
+  constexpr int kRawStages = R::kRawStages;
+  constexpr int kAStages = R::kAStages;
+  constexpr int kBGroup = R::kBGroup;
+  constexpr int kBStages = R::kBStages;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -265,7 +276,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int byte0 = tile0 * (BK * WBITS / 8);
       for (int r = 0; r < n_raw; ++r) {
         const int s = r % kRawStages;
-        ptx::mbar_wait(&raw_empty[s], ((r / kRawStages) & 1) ^ 1, abort_flag, p.err_word, ptx::kErrWaitEmpty);
+        ptx::mbar_wait<64>(&raw_empty[s], ((r / kRawStages) & 1) ^ 1, abort_flag, p.err_word, ptx::kErrWaitEmpty);
         stamp(p, 3, ti);
         ptx::mbar_expect_tx(&raw_full[s], kRawBytes);
         ptx::tma_load_2d(raw_base + (size_t)s * kRawBytes, &map_w, &raw_full[s], byte0 + r * 128, (int32_t)n0);
@@ -276,7 +287,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (lane == 0) {
       for (int gidx = 0; gidx < n_groups; ++gidx) {
         const int s = gidx % kBStages;
-        ptx::mbar_wait(&b_empty[s], ((gidx / kBStages) & 1) ^ 1, abort_flag, p.err_word, ptx::kErrWaitEmpty);
+        ptx::mbar_wait<64>(&b_empty[s], ((gidx / kBStages) & 1) ^ 1, abort_flag, p.err_word, ptx::kErrWaitEmpty);
         int cnt = my_tiles - gidx * kBGroup;
         if (cnt > kBGroup) cnt = kBGroup;
         ptx::mbar_expect_tx(&b_full[s], (uint32_t)cnt * kBBytes);
@@ -287,7 +298,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    // The whole warp walks the loop and waits together; one lane issues.  (A warp left diverged for
+    // the length of the kernel - one lane looping, 31 parked at the final barrier - runs that lane at a
+    // fraction of the normal issue rate.)
+    {
+      // Both operands carry the activation type: kind::f16 with A = f16 and B = bf16 is rejected by the
+      // hardware (illegal instruction on B200), so int8 weights cannot take the cheaper fp16 conversion
+      // when the activations are bf16.
       constexpr uint32_t fmt = kIsBf16 ? 1u : 0u;
       constexpr uint32_t idesc = ptx::make_idesc(/*f32*/ 1, fmt, fmt, BMW, MP);
       // descriptor halves: the high word is constant, the low word is the tile address >> 4
@@ -295,18 +312,20 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t a_lo0 = (uint32_t)ptx::make_sw128_kmajor_desc(ptx::smem_u32(a_base));
       const uint32_t b_lo0 = (uint32_t)ptx::make_sw128_kmajor_desc(ptx::smem_u32(b_base));
       int blk = 0, in_blk = 0, ti = 0;
+      const uint32_t leader = lane == 0 ? 1u : 0u;
       for (int t = 0; t < my_tiles; ++t) {
         const int buf = blk & 1;
         if (in_blk == 0) {
           ptx::mbar_wait(&acc_empty[buf], ((blk >> 1) & 1) ^ 1, abort_flag, p.err_word, ptx::kErrWaitTmemEmpty);
+          ptx::tcgen05_fence_after();  // the drain warps' tcgen05.ld of this buffer precede the overwrite
         }
         const int sa = t % kAStages;
         const int gb = t / kBGroup, sb = gb % kBStages, jb = t % kBGroup;
         if (jb == 0) ptx::mbar_wait(&b_full[sb], (gb / kBStages) & 1, abort_flag, p.err_word, ptx::kErrWaitFull);
-        stamp(p, 1, ti);
+        if (p.trace && lane == 0) stamp(p, 1, ti);
         ptx::mbar_wait(&a_full[sa], (t / kAStages) & 1, abort_flag, p.err_word, ptx::kErrWaitConv);
-        ptx::tcgen05_fence_after();
-        stamp(p, 1, ti);
+        if (p.trace && lane == 0) stamp(p, 1, ti);
+        const bool last_in_block = (in_blk + 1 == p.tiles_per_block) || (t == my_tiles - 1);
         const uint32_t a_lo = a_lo0 + (uint32_t)sa * (kABytes >> 4);
         const uint32_t b_lo = b_lo0 + (uint32_t)(sb * kBGroup + jb) * (kBBytes >> 4);
         const uint32_t d_tmem = tmem_base + buf * MP;
@@ -314,68 +333,77 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int k = 0; k < BK / UMMA_K; ++k) {
           const uint64_t ad = ((uint64_t)desc_hi << 32) | (uint64_t)(a_lo + k * (UMMA_K * 2 >> 4));
           const uint64_t bd = ((uint64_t)desc_hi << 32) | (uint64_t)(b_lo + k * (UMMA_K * 2 >> 4));
-          ptx::mma_f16_ss(d_tmem, ad, bd, idesc, (in_blk | k) != 0 ? 1u : 0u);
+          ptx::mma_f16_ss_pred(d_tmem, ad, bd, idesc, (in_blk | k) != 0 ? 1u : 0u, leader);
         }
-        ptx::mma_commit(&a_empty[sa]);
-        if (jb == kBGroup - 1 || t == my_tiles - 1) ptx::mma_commit(&b_empty[sb]);
+        ptx::mma_commit_pred(&a_empty[sa], leader);
+        if (jb == kBGroup - 1 || t == my_tiles - 1) ptx::mma_commit_pred(&b_empty[sb], leader);
+        if (last_in_block) ptx::mma_commit_pred(&acc_full[buf], leader);
+        if (p.trace && lane == 0) stamp(p, 1, ti);
         ++in_blk;
-        if (in_blk == p.tiles_per_block || t == my_tiles - 1) {
-          ptx::mma_commit(&acc_full[buf]);
+        if (last_in_block) {
           in_blk = 0;
           ++blk;
         }
-        stamp(p, 1, ti);
       }
     }
-  } else if (warp >= 4 && warp < 4 + kDequantWarps) {
+  } else if (warp >= 4 && warp < 12 && (warp & 3) != 1) {
     // ---------------- dequant: warp d owns operand tiles d, d+8, ...; lane owns rows lane+32i ----------------
-    // Each active warp owns ONE ring slot (slot == warp index), so a warp is never more than one
-    // barrier phase ahead of the slot it waits on: with fewer slots than warps, the surplus warps idle.
-    // (A warp two generations ahead of a slot would read the parity of an older phase as "done".)
-    constexpr int kActive = kAStages < kDequantWarps ? kAStages : kDequantWarps;
-    static_assert(kAStages % kActive == 0, "operand ring slots must map one-to-one onto converting warps");
-    const int dw = warp - 4;
+    // Each active warp owns ONE ring slot (slot == warp index), see Rings.
+    // The converting warps sit on the three scheduler partitions the MMA issuer (warp 1) is NOT on:
+    // they are ALU-saturated and would starve its few, latency-critical instructions of issue slots.
+    constexpr int kActive = kDequantWarps;
+    constexpr int kChunks = (WBITS == 4) ? 2 : 4;  // 16-byte raw chunks per row per operand tile
+    const int dw = (warp - 4) - ((warp - 4) + 3) / 4;  // warps 4,6,7,8,10,11 -> 0..5
     int ti = 0;
     const bool tracer = (warp == 4 && lane == 0);
-    for (int t = dw; t < my_tiles && dw < kActive; t += kActive) {
+    for (int t = dw; t < my_tiles; t += kActive) {
       const int rs = t / TPR, a = t % TPR;
       const int s = rs % kRawStages, sa = t % kAStages;
       if (tracer) stamp(p, 0, ti);
-      ptx::mbar_wait_warp(&raw_full[s], (rs / kRawStages) & 1, abort_flag, p.err_word, ptx::kErrWaitRaw);
-      ptx::mbar_wait_warp(&a_empty[sa], ((t / kAStages) & 1) ^ 1, abort_flag, p.err_word, ptx::kErrWaitEmpty);
+      ptx::mbar_wait_warp<64>(&a_empty[sa], ((t / kAStages) & 1) ^ 1, abort_flag, p.err_word, ptx::kErrWaitEmpty);
+      ptx::mbar_wait_warp<64>(&raw_full[s], (rs / kRawStages) & 1, abort_flag, p.err_word, ptx::kErrWaitRaw);
       if (tracer) stamp(p, 0, ti);
-      const uint32_t raw_tile = ptx::smem_u32(raw_base + (size_t)s * kRawBytes);
-      const uint32_t a_tile = ptx::smem_u32(a_base + (size_t)sa * kABytes);
+      const uint8_t* raw_tile = raw_base + (size_t)s * kRawBytes;
+      uint8_t* a_tile = a_base + (size_t)sa * kABytes;
+      // all loads of the tile first (plain loads: the compiler may keep them in flight together), then
+      // convert and store; the barrier waits above and the proxy fence below order them
+      uint4 rawv[4][kChunks];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int r = lane + 32 * i;
-        const uint32_t sw = (uint32_t)(r & 7);
-        const uint32_t raw_row = raw_tile + r * 128, a_row = a_tile + r * 128;
+#pragma unroll
+        for (int jj = 0; jj < kChunks; ++jj)
+          rawv[i][jj] = *reinterpret_cast<const uint4*>(raw_tile + r * 128 + (((kChunks * a + jj) ^ (r & 7)) << 4));
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = lane + 32 * i;
+        const int sw = r & 7;
+        uint8_t* a_row = a_tile + r * 128;
         if (WBITS == 4) {
           // two raw chunks (32 nibbles each) -> eight operand chunks (8 values each)
 #pragma unroll
           for (int jj = 0; jj < 2; ++jj) {
-            const uint4 v = lds128(raw_row + (((uint32_t)(2 * a + jj) ^ sw) << 4));
-            const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+            const uint32_t words[4] = {rawv[i][jj].x, rawv[i][jj].y, rawv[i][jj].z, rawv[i][jj].w};
 #pragma unroll
             for (int wi = 0; wi < 4; ++wi) {
               uint32_t pk[4];
               cvt_s4x8<XT>(words[wi], pk);
-              sts128(a_row + (((uint32_t)(jj * 4 + wi) ^ sw) << 4), pk[0], pk[1], pk[2], pk[3]);
+              *reinterpret_cast<uint4*>(a_row + (((jj * 4 + wi) ^ sw) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
             }
           }
         } else {
           // four raw chunks (16 bytes each) -> eight operand chunks
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj) {
-            const uint4 v = lds128(raw_row + (((uint32_t)(4 * a + jj) ^ sw) << 4));
+            const uint4 v = rawv[i][jj];
             uint32_t q0, q1, q2, q3;
             cvt_s8x4<XT>(v.x, q0, q1);
             cvt_s8x4<XT>(v.y, q2, q3);
-            sts128(a_row + (((uint32_t)(jj * 2) ^ sw) << 4), q0, q1, q2, q3);
+            *reinterpret_cast<uint4*>(a_row + (((jj * 2) ^ sw) << 4)) = make_uint4(q0, q1, q2, q3);
             cvt_s8x4<XT>(v.z, q0, q1);
             cvt_s8x4<XT>(v.w, q2, q3);
-            sts128(a_row + (((uint32_t)(jj * 2 + 1) ^ sw) << 4), q0, q1, q2, q3);
+            *reinterpret_cast<uint4*>(a_row + (((jj * 2 + 1) ^ sw) << 4)) = make_uint4(q0, q1, q2, q3);
           }
         }
       }
@@ -406,7 +434,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int buf = b & 1;
         const float s = n_ok ? (p.blockwise ? __ldg(p.scale + (int64_t)(block0 + b) * p.N + n) : 1.f) : 0.f;
         if (tracer) stamp(p, 2, ti);
-        ptx::mbar_wait_warp(&acc_full[buf], (b >> 1) & 1, abort_flag, p.err_word, ptx::kErrWaitTmemFull);
+        ptx::mbar_wait_warp<32>(&acc_full[buf], (b >> 1) & 1, abort_flag, p.err_word, ptx::kErrWaitTmemFull);
         ptx::tcgen05_fence_after();
         if (tracer) stamp(p, 2, ti);
 #pragma unroll
@@ -493,7 +521,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 template <int WBITS, typename XT, int MP, bool KSPLIT>
 int launch_one(const CUtensorMap& map_w, const CUtensorMap& map_x, const Params& p, dim3 grid, cudaStream_t st) {
   auto kern = mixed_tc_kernel<WBITS, XT, MP, KSPLIT>;
-  constexpr size_t smem = smem_bytes<MP>();
+  constexpr size_t smem = smem_bytes<WBITS, MP>();
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);

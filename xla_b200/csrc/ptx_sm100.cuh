@@ -84,12 +84,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait.  `abort_flag` is a CTA-shared word; `err_word` the library's global error word.
 // The fast path is a bare try_wait loop; the SM cycle counter is looked at only once every 4096
 // polls (a %globaltimer read per wait costs about a microsecond and would dominate short waits).
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
                                           volatile uint32_t* abort_flag, uint32_t* err_word,
                                           uint32_t code) {
   uint32_t spins = 0;
   long long t0 = 0;
   while (!mbar_try_wait(bar, parity)) {
+    if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);  // back off: pollers share the barrier unit with the MMA issuer
     if ((++spins & 0xfff) == 0) {
       if (*abort_flag) return false;
       const long long now = clock64();
@@ -107,11 +109,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
 
 // Whole-warp wait: lane 0 polls, the rest of the warp parks at the warp barrier.  Keeps 31 of 32
 // lanes from hammering the same mbarrier word while the single-thread MMA issuer needs that unit.
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity,
                                                volatile uint32_t* abort_flag, uint32_t* err_word,
                                                uint32_t code) {
   bool ok = true;
-  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, err_word, code);
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait<SLEEP_NS>(bar, parity, abort_flag, err_word, code);
   __syncwarp();
   return ok;
 }
@@ -210,6 +213,45 @@ __device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uin
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
       "}" ::"r"(d_tmem),
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Predicated forms: every lane of the issuing warp executes the same instruction stream and only the
+// lane with `leader` != 0 takes effect.  Keeps the issuing warp converged (no branch around the MMA).
+__device__ __forceinline__ void mma_f16_ss_pred(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                uint32_t idesc, uint32_t accumulate, uint32_t leader) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(leader)
+      : "memory");
+}
+
+__device__ __forceinline__ void mma_i8_ss_pred(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                               uint32_t idesc, uint32_t accumulate, uint32_t leader) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
+      "}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(leader)
+      : "memory");
+}
+
+__device__ __forceinline__ void mma_commit_pred(uint64_t* bar, uint32_t leader) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred q;\n\t"
+      "setp.ne.b32 q, %1, 0;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+      "}" ::"r"(smem_u32(bar)),
+      "r"(leader)
       : "memory");
 }
 

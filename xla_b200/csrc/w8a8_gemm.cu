@@ -123,8 +123,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    // All 32 lanes walk the loop and wait together; the MMA and commit instructions are predicated on
+    // lane 0, so the warp never diverges around them.
+    {
       constexpr uint32_t idesc = ptx::make_idesc(/*s32*/ 2, /*s8*/ 1, /*s8*/ 1, BM, BN);
+      const uint32_t leader = lane == 0 ? 1u : 0u;
+      const uint32_t desc_hi = (uint32_t)(ptx::make_sw128_kmajor_desc(0) >> 32);
+      const uint32_t lo0 = (uint32_t)ptx::make_sw128_kmajor_desc(ptx::smem_u32(stage_base));
       uint32_t it = 0, tcount = 0;
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
         const int ab = tcount % kAccBufs;
@@ -136,18 +141,17 @@ __global__ void __launch_bounds__(kThreads, 1)
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
           ptx::mbar_wait(&full[s], ph, abort_flag, p.err_word, ptx::kErrWaitFull);
-          ptx::tcgen05_fence_after();
-          const uint32_t a_addr = ptx::smem_u32(stage_base + (size_t)s * kStageBytes);
-          const uint32_t b_addr = a_addr + kStageA;
+          const uint32_t a_lo = lo0 + (uint32_t)s * (kStageBytes >> 4);
+          const uint32_t b_lo = a_lo + (kStageA >> 4);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t a_desc = ptx::make_sw128_kmajor_desc(a_addr + k * UMMA_K);
-            const uint64_t b_desc = ptx::make_sw128_kmajor_desc(b_addr + k * UMMA_K);
-            ptx::mma_i8_ss(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
+            const uint64_t a_desc = ((uint64_t)desc_hi << 32) | (uint64_t)(a_lo + k * (UMMA_K >> 4));
+            const uint64_t b_desc = ((uint64_t)desc_hi << 32) | (uint64_t)(b_lo + k * (UMMA_K >> 4));
+            ptx::mma_i8_ss_pred(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u, leader);
           }
-          ptx::mma_commit(&empty[s]);  // frees the stage once these MMAs have read it
+          ptx::mma_commit_pred(&empty[s], leader);  // frees the stage once these MMAs have read it
         }
-        ptx::mma_commit(&tmem_full[ab]);
+        ptx::mma_commit_pred(&tmem_full[ab], leader);
       }
     }
   } else {
