@@ -8,8 +8,9 @@
 // For bf16 activations the two roundings to bf16 are not optional: dropping the second one
 // changes 0.6 % of the entries on N(0,1) data with outliers.
 //
-// One CTA per activation row.  The row is read twice (amax, then quantize); the second read is
-// served by L1/L2, so HBM sees each activation once: 2 or 4 bytes in, 1 byte out per element.
+// One CTA per activation row.  bf16 rows of up to 8192 elements stay in registers between the two
+// phases (amax, then quantize); other shapes read the row twice, the second time from L1/L2.  Either
+// way HBM sees each activation once: 2 or 4 bytes in, 1 byte out per element.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -139,6 +140,92 @@ __global__ void __launch_bounds__(kThreads)
   }
 }
 
+
+// ---- bf16 fast path: the row lives in registers; one global read, one global write -------------------
+//
+// amax is taken on the bit patterns: for non-negative floats the integer order is the float order, and
+// a NaN pattern is larger than every number, so NaN propagates like torch.amax without extra tests.
+//
+// The quotient x / scale must be the correctly rounded fp32 quotient (it is rounded to bf16 next and
+// ties decide).  One Newton step on q0 = x * (1/scale) gives it: both operands have 8-bit significands,
+// so the exact quotient is either a tie (exactly representable: the step lands on it) or at least
+// 2^-17 away from any bf16 rounding boundary, far more than the error of q0.
+template <int CHUNKS>
+__global__ void __launch_bounds__(kThreads)
+    quantize_rows_bf16_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__ xq,
+                              float* __restrict__ x_scale, int32_t* __restrict__ rowsum, int64_t K,
+                              int saturate) {
+  __shared__ uint32_t s_red[kThreads / 32];
+  __shared__ int s_isum[kThreads / 32];
+  const int64_t m = blockIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nvec = (int)(K >> 3);  // 16-byte chunks (8 bf16) in the row
+  const uint4* rv = reinterpret_cast<const uint4*>(x + m * K);
+  uint4 v[CHUNKS];
+  uint32_t amax_bits = 0;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int i = tid + c * kThreads;
+    v[c] = make_uint4(0, 0, 0, 0);
+    if (i < nvec) v[c] = rv[i];
+    const uint32_t w[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      amax_bits = max(amax_bits, w[j] & 0x7fffu);
+      amax_bits = max(amax_bits, (w[j] >> 16) & 0x7fffu);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, o));
+  if (lane == 0) s_red[warp] = amax_bits;
+  __syncthreads();
+  uint32_t a = s_red[0];
+#pragma unroll
+  for (int i = 1; i < kThreads / 32; ++i) a = max(a, s_red[i]);
+  const float amax = __uint_as_float(a << 16);
+  const float scale = round_to<__nv_bfloat16>(__fdiv_rn(amax, 127.0f));
+  if (tid == 0) x_scale[m] = scale;
+  const float rcp = __frcp_rn(scale);
+  // scale == 0 (all-zero row), inf or NaN: the Newton step is not valid there; fall back to IEEE division
+  const bool regular = scale > 1e-30f && scale < 1e30f;
+
+  int isum = 0;
+  uint2* qv = reinterpret_cast<uint2*>(xq + m * K);
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int i = tid + c * kThreads;
+    const uint32_t w[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
+    uint32_t packed[2] = {0, 0};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float xv = __uint_as_float((j & 1) ? (w[j >> 1] & 0xffff0000u) : (w[j >> 1] << 16));
+      float q;
+      if (regular) {
+        const float q0 = xv * rcp;
+        const float r = fmaf(-q0, scale, xv);
+        q = fmaf(r, rcp, q0);
+      } else {
+        q = __fdiv_rn(xv, scale);
+      }
+      const int8_t qi = to_int8(rintf(round_to<__nv_bfloat16>(q)), saturate != 0);
+      isum += qi;
+      packed[j >> 2] |= ((uint32_t)(uint8_t)qi) << (8 * (j & 3));
+    }
+    if (i < nvec) qv[i] = make_uint2(packed[0], packed[1]);
+  }
+  if (rowsum) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) isum += __shfl_xor_sync(0xffffffffu, isum, o);
+    if (lane == 0) s_isum[warp] = isum;
+    __syncthreads();
+    if (tid == 0) {
+      int t = 0;
+      for (int i = 0; i < kThreads / 32; ++i) t += s_isum[i];
+      rowsum[m] = t;
+    }
+  }
+}
+
 }  // namespace
 
 int launch_quantize_activation(const void* x, int x_dt, int8_t* xq, float* x_scale,
@@ -146,6 +233,17 @@ int launch_quantize_activation(const void* x, int x_dt, int8_t* xq, float* x_sca
                                cudaStream_t st) {
   if (M == 0) return QMM_OK;
   if (M > 2147483647LL) return fail(QMM_ERR_UNSUPPORTED, "quantize_activation: M too large");
+  if (x_dt == QMM_BF16 && K % 8 == 0 && K <= 8 * 4 * kThreads && aligned(x, 16) && aligned(xq, 8)) {
+    const __nv_bfloat16* xp = reinterpret_cast<const __nv_bfloat16*>(x);
+    const int chunks = (int)ceil_div(K / 8, kThreads);
+    if (chunks <= 1)
+      quantize_rows_bf16_kernel<1><<<(unsigned)M, kThreads, 0, st>>>(xp, xq, x_scale, rowsum, K, saturate);
+    else if (chunks == 2)
+      quantize_rows_bf16_kernel<2><<<(unsigned)M, kThreads, 0, st>>>(xp, xq, x_scale, rowsum, K, saturate);
+    else
+      quantize_rows_bf16_kernel<4><<<(unsigned)M, kThreads, 0, st>>>(xp, xq, x_scale, rowsum, K, saturate);
+    return check_launch("quantize_rows_bf16_kernel");
+  }
   QMM_DISPATCH_DTYPE(x_dt, T, {
     constexpr int VEC = 16 / sizeof(T);
     const int vec_ok = (K % VEC == 0) && aligned(x, 16) && aligned(xq, VEC) ? 1 : 0;

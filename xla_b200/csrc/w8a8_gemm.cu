@@ -24,14 +24,18 @@ constexpr int BM = 128;       // activation rows per tile  (UMMA M)
 constexpr int BN = 256;       // weight rows per tile      (UMMA N)
 constexpr int BK = 128;       // int8 elements per stage = one 128-byte swizzle row
 constexpr int UMMA_K = 32;    // kind::i8
-constexpr int kStages = 4;
+constexpr int kStages = 3;
 constexpr int kAccBufs = 2;
 constexpr int kThreads = 192;
 constexpr uint32_t kStageA = BM * BK;           // 16 KB
 constexpr uint32_t kStageB = BN * BK;           // 32 KB
 constexpr uint32_t kStageBytes = kStageA + kStageB;
 constexpr uint32_t kTmemCols = kAccBufs * BN;   // 512
-constexpr size_t kSmemBytes = 1024 /*align slack*/ + (size_t)kStages * kStageBytes + 256;
+constexpr uint32_t kOutBoxCols = 64;                      // 16-bit outputs: 64 columns = one 128-byte swizzle row
+constexpr uint32_t kOutBoxBytes = BM * 128;               // 16 KB per [128 x 64] box
+constexpr uint32_t kOutStaging = (BN / kOutBoxCols) * kOutBoxBytes;  // 64 KB: the whole 128 x 256 tile
+constexpr uint32_t kScaleBytes = 2 * BN * 4;              // w_scale and zero point of the tile's columns
+constexpr size_t kSmemBytes = 1024 /*align slack*/ + (size_t)kStages * kStageBytes + kOutStaging + kScaleBytes + 256;
 
 struct Params {
   const float* w_scale;
@@ -43,6 +47,7 @@ struct Params {
   int out_dt;
   int64_t M, N, K;
   int tiles_m, tiles_n, k_blocks;
+  int tma_store;  // 16-bit output staged in shared memory and written with TMA
   uint32_t* err_word;
 };
 
@@ -64,12 +69,15 @@ __device__ __forceinline__ void store_row_chunk(OT* dst, const float* v, int nco
 
 __global__ void __launch_bounds__(kThreads, 1)
     w8a8_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                   const Params p) {
+                   const __grid_constant__ CUtensorMap map_out, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* stage_base = smem;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kStages * kStageBytes);
+  uint8_t* staging = smem + (size_t)kStages * kStageBytes;               // [4 boxes][128 rows][128 B], swizzled
+  float* s_ws = reinterpret_cast<float*>(staging + kOutStaging);         // [BN] weight scales of the tile
+  float* s_zp = s_ws + BN;                                               // [BN] zero points (or 0)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + kOutStaging + kScaleBytes);
   uint64_t* full = bars;                       // [kStages]
   uint64_t* empty = bars + kStages;            // [kStages]
   uint64_t* tmem_full = bars + 2 * kStages;    // [kAccBufs]
@@ -169,6 +177,66 @@ __global__ void __launch_bounds__(kThreads, 1)
       const float xs = (row_ok && p.out) ? p.x_scale[m] : 0.f;
       const int32_t rs = (row_ok && p.rowsum) ? p.rowsum[m] : 0;
       const uint32_t taddr = tmem_base + ab * BN + ((uint32_t)(quad * 32) << 16);
+      if (p.tma_store) {
+        // ---- 16-bit output: dequantise into a swizzled shared-memory tile, one TMA store per 64 columns ----
+        const int e = threadIdx.x - 64;  // 0..127 among the epilogue threads
+        if (e == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // staging free again
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        for (int j = e; j < BN; j += 128) {
+          const int64_t n = (int64_t)tn * BN + j;
+          s_ws[j] = n < p.N ? __ldg(p.w_scale + n) : 0.f;
+          s_zp[j] = (p.zp && n < p.N) ? __ldg(p.zp + n) : 0.f;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int rl = quad * 32 + lane;  // row inside the tile
+        const uint32_t row_base = ptx::smem_u32(staging) + rl * 128;
+        const uint32_t sw = (uint32_t)(rl & 7);
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32b_x32(taddr + c * 32, r);
+          ptx::tmem_ld_wait();
+          uint32_t pk[16];
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const float v0 = w8a8_dequant((int32_t)r[j], s_ws[c * 32 + j], p.zp ? &s_zp[c * 32 + j] : nullptr, rs, xs);
+            const float v1 = w8a8_dequant((int32_t)r[j + 1], s_ws[c * 32 + j + 1], p.zp ? &s_zp[c * 32 + j + 1] : nullptr, rs, xs);
+            if (p.out_dt == QMM_BF16) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+              pk[j >> 1] = *reinterpret_cast<uint32_t*>(&h);
+            } else {
+              __half2 h = __floats2half2_rn(v0, v1);
+              pk[j >> 1] = *reinterpret_cast<uint32_t*>(&h);
+            }
+          }
+          // 32 columns = 64 bytes = four 16-byte pieces of box (c / 2), pieces (c & 1) * 4 .. + 3
+          const uint32_t box = row_base + (uint32_t)(c >> 1) * kOutBoxBytes;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t piece = (uint32_t)((c & 1) * 4 + i) ^ sw;
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(box + (piece << 4)), "r"(pk[4 * i]),
+                         "r"(pk[4 * i + 1]), "r"(pk[4 * i + 2]), "r"(pk[4 * i + 3])
+                         : "memory");
+          }
+        }
+        ptx::tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&tmem_empty[ab]);
+        ptx::fence_proxy_async_smem();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (e == 0) {
+#pragma unroll
+          for (int b = 0; b < BN / (int)kOutBoxCols; ++b) {
+            const int32_t c0 = tn * BN + b * (int)kOutBoxCols;
+            if (c0 < p.N)
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(&map_out),
+                           "r"(ptx::smem_u32(staging) + b * kOutBoxBytes), "r"(c0), "r"(tm * BM)
+                           : "memory");
+          }
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -208,6 +276,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&tmem_empty[ab]);
     }
+    // the staging tile must outlive the last TMA store that reads it
+    if (p.tma_store && threadIdx.x == 64) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
   ptx::tcgen05_fence_before();
@@ -252,7 +322,17 @@ int launch_w8a8_tc(const int8_t* xq, const int8_t* w, const float* w_scale, cons
     if (e != cudaSuccess) return fail(QMM_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     if (dev >= 0 && dev < 64) attr_set[dev] = true;
   }
+  // 16-bit outputs go through a shared-memory tile and TMA stores (row pitch must be a multiple of 16 B)
+  const bool tma_store = out && !acc_out && out_dt != QMM_F32 && (N % 8 == 0) && aligned(out, 16);
+  CUtensorMap map_out;
+  if (tma_store) {
+    rc = encode_tmap_2d(&map_out, out, 2, true, (uint64_t)M, (uint64_t)N, BM, kOutBoxCols);
+    if (rc != QMM_OK) return rc;
+  } else {
+    map_out = map_x;  // unused by the kernel on this path
+  }
   Params p;
+  p.tma_store = tma_store ? 1 : 0;
   p.w_scale = w_scale;
   p.zp = zp;
   p.x_scale = x_scale;
@@ -269,7 +349,7 @@ int launch_w8a8_tc(const int8_t* xq, const int8_t* w, const float* w_scale, cons
   p.err_word = device_error_word();
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  w8a8_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(map_x, map_w, p);
+  w8a8_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(map_x, map_w, map_out, p);
   return check_launch("w8a8_tc_kernel");
 }
 
