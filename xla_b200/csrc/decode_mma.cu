@@ -146,7 +146,25 @@ __global__ void __launch_bounds__(WARPS * 32)
     }
   const uint32_t ones[4] = {kOnes, kOnes, kOnes, kOnes};
 
-  // the weights of this warp's next step are in flight while the current one is converted
+  // Software pipeline, one step deep: the weights of this warp's next step are in flight while the
+  // current step is converted and multiplied.  (Prefetching the activations as well costs 24 registers
+  // and measured slower: they come from L1.)
+  constexpr bool kPrefetchX = false;
+  auto load_x = [&](int step, uint32_t (&dst)[NT][XREGS]) {
+#pragma unroll
+    for (int i = 0; i < NT; ++i) {
+      const uint4* xp = reinterpret_cast<const uint4*>(xrow[i] + (int64_t)step * VPS);
+#pragma unroll
+      for (int q = 0; q < XREGS / 4; ++q) {
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (tok_ok[i]) v = __ldg(xp + q);
+        dst[i][4 * q] = v.x;
+        dst[i][4 * q + 1] = v.y;
+        dst[i][4 * q + 2] = v.z;
+        dst[i][4 * q + 3] = v.w;
+      }
+    }
+  };
   int s = warp;
   uint4 wn[2 * RG];
 #pragma unroll
@@ -154,14 +172,29 @@ __global__ void __launch_bounds__(WARPS * 32)
     wn[r] = make_uint4(0, 0, 0, 0);
     if (s < steps) wn[r] = ld_stream_u4(wrow[r] + (int64_t)s * 64);
   }
+  // Programmatic dependent launch: the weights are static, so their first loads may overlap the tail
+  // of the previous kernel in the stream; everything that depends on that kernel (the activations)
+  // and every store of this kernel come after the wait.  Both are no-ops in an ordinary launch.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  uint32_t xn[NT][XREGS];
+  if (kPrefetchX && s < steps) load_x(s, xn);
   for (; s < steps; s += WARPS) {
     uint4 wc[2 * RG];
 #pragma unroll
     for (int r = 0; r < 2 * RG; ++r) wc[r] = wn[r];
+    uint32_t xr[NT][XREGS];
+    if (kPrefetchX) {
+#pragma unroll
+      for (int i = 0; i < NT; ++i)
+#pragma unroll
+        for (int q = 0; q < XREGS; ++q) xr[i][q] = xn[i][q];
+    }
     const int sn = s + WARPS;
     if (sn < steps) {
 #pragma unroll
       for (int r = 0; r < 2 * RG; ++r) wn[r] = ld_stream_u4(wrow[r] + (int64_t)sn * 64);
+      if (kPrefetchX) load_x(sn, xn);
     }
     // fold after this step?  (blockwise: this warp's next step belongs to another block)
     bool fold = true;
@@ -177,20 +210,7 @@ __global__ void __launch_bounds__(WARPS * 32)
         for (int r = 0; r < 2 * RG; ++r) sc[r] = __ldg(srow[r] + (int64_t)b * N);
       }
     }
-    uint32_t xr[NT][XREGS];
-#pragma unroll
-    for (int i = 0; i < NT; ++i) {
-      const uint4* xp = reinterpret_cast<const uint4*>(xrow[i] + (int64_t)s * VPS);
-#pragma unroll
-      for (int q = 0; q < XREGS / 4; ++q) {
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (tok_ok[i]) v = __ldg(xp + q);
-        xr[i][4 * q] = v.x;
-        xr[i][4 * q + 1] = v.y;
-        xr[i][4 * q + 2] = v.z;
-        xr[i][4 * q + 3] = v.w;
-      }
-    }
+    if (!kPrefetchX) load_x(s, xr);
 #pragma unroll
     for (int wi = 0; wi < 4; ++wi) {
       if constexpr (WBITS == 4) {
@@ -276,6 +296,23 @@ __global__ void __launch_bounds__(WARPS * 32)
   }
 }
 
+// Launch with programmatic stream serialization: this kernel may be scheduled while the previous
+// kernel of the stream drains, and parks at its griddepcontrol.wait until that kernel has finished.
+template <typename Kernel, typename... Args>
+cudaError_t launch_pdl(Kernel kern, unsigned grid, unsigned block, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
 template <int WBITS, typename XT>
 int launch_nt(const void* x, const void* w, const float* scale, void* out, int out_dt, int64_t M, int64_t N,
               int64_t K, int64_t block_size, cudaStream_t st) {
@@ -290,17 +327,22 @@ int launch_nt(const void* x, const void* w, const float* scale, void* out, int o
   const XT* xp = reinterpret_cast<const XT*>(x);
   const uint8_t* wp = reinterpret_cast<const uint8_t*>(w);
 #define QMM_DECODE_LAUNCH(NT, RG, WARPS)                                                                        \
-  decode_mma_kernel<WBITS, XT, NT, RG, WARPS><<<(unsigned)ceil_div(N, 16 * RG), WARPS * 32, 0, st>>>(           \
-      xp, wp, scale, out, out_dt, (int)M, N, K, spb, shift, bw)
+  launch_pdl(decode_mma_kernel<WBITS, XT, NT, RG, WARPS>, (unsigned)ceil_div(N, 16 * RG), WARPS * 32, st, xp, wp, \
+             scale, out, out_dt, (int)M, N, K, spb, shift, bw)
   // measured on B200 (w [14336,4096] int4): 16 rows per CTA is best for one token tile; with two or four
   // tiles the activation traffic through L1 dominates and 32 rows per CTA (activation registers reused
   // for two row groups) wins
+  cudaError_t err;
   if (M <= 8)
-    QMM_DECODE_LAUNCH(1, 1, 4);
+    err = QMM_DECODE_LAUNCH(1, 1, 4);
   else if (M <= 16)
-    QMM_DECODE_LAUNCH(2, 2, 4);
+    err = QMM_DECODE_LAUNCH(2, 2, 4);
   else
-    QMM_DECODE_LAUNCH(4, 2, 4);
+    err = QMM_DECODE_LAUNCH(4, 2, 4);
+  if (err != cudaSuccess) {
+    cudaGetLastError();
+    return fail(QMM_ERR_LAUNCH, "decode_mma_kernel launch: %s", cudaGetErrorString(err));
+  }
 #undef QMM_DECODE_LAUNCH
   return check_launch("decode_mma_kernel");
 }
