@@ -469,6 +469,10 @@ def run_ours(args, rank, world, local_rank):
                          "algorithmic_bytes": wl.bytes_per_launch(m), "gb_per_s": gbs,
                          "frac_of_hbm_peak": gbs / peaks["hbm_gbs"], "tflops": wl.flops_per_launch(m) / (ms * 1e-3) / 1e12})
     dom = max(per_kernel, key=lambda r: r["us_per_launch"])
+    # dram__bytes_read.sum + dram__bytes_write.sum per launch of the headline kernel, from the ncu captures
+    # summarised in profiles/decode_mma_kernel__w4a16_decode_14336x4096.md (the writes are below 0.1 MB:
+    # the bf16 output is still in L2 when the kernel ends)
+    ncu_traffic = {1: 31.21e6, 8: 31.27e6, 32: 31.48e6}
     e2e_tokens = world * args.steps * e2e_reps * sum(wl.MS)
     line = {
         "metric": "qlinear_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
@@ -479,7 +483,9 @@ def run_ours(args, rank, world, local_rank):
                    "parallelism": f"dp{world} replicas (no data-path collective)" if world > 1 else "single GPU",
                    "timing": "CUDA events on the launch stream; steps are CUDA-graph replays"},
         "roofline": {"bound": "hbm", "achieved": dom["gb_per_s"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": dom["gb_per_s"] / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                     "frac": dom["gb_per_s"] / peaks["hbm_gbs"],
+                     "traffic": ncu_traffic.get(dom["M"]) if dom["kernel"] == "mma" else None,
+                     "peak_source": peaks["source"],
                      "kernel": f"{dom['kernel']} M={dom['M']}"},
         "per_kernel": per_kernel,
         "e2e": {"value": e2e_tokens / (e2e_ms * 1e-3), "unit": "tokens/s",

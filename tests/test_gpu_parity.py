@@ -480,3 +480,68 @@ def test_mma_w8a16_per_channel(M, xdtype):
   assert qo.max_abs_rel(out, qo.quantized_matmul(x, w, s, dot_round=None)) < TOL_F32
   with pytest.raises(NotImplementedError):
     op(cu(qc.activations(g, 33, K, dtype=xdtype)), cu(w), cu(s), variant="mma")
+
+
+# ---------------------------------------------------------------------------------------------
+# the reference's module-level tests, replayed on the GPU (test/quantized_ops/test_quantized_matmul.py)
+# ---------------------------------------------------------------------------------------------
+
+
+def _cos(a, b):
+  a, b = a.flatten().double().cpu(), b.flatten().double().cpu()
+  return float(torch.dot(a, b) / (a.norm() * b.norm()))
+
+
+@pytest.mark.parametrize("quantize_activation", [False, True])
+def test_reference_style_q_linear_module_per_channel(quantize_activation):
+  # :112-126 -- fp Linear(5, 8) vs the quantized module, atol 0.01
+  from xla_b200 import weight_prep as wp
+  torch.manual_seed(123456)
+  lin = torch.nn.Linear(5, 8, bias=False)
+  x = torch.randn(3, 5)
+  out_fp = lin(x)
+  m = wp.quantize_linear(lin, quantize_activation=quantize_activation).to(DEV)
+  out_q = m(x.to(DEV))
+  assert torch.allclose(out_fp, out_q.cpu(), atol=0.02 if quantize_activation else 0.01)
+
+
+@pytest.mark.parametrize("n_bits,block_size,symmetric,qa", [(4, -1, True, False), (8, 2, True, False), (4, 2, True, False),
+                                                          (8, -1, False, False), (8, -1, False, True), (4, -1, False, False),
+                                                          (8, 2, False, False)])
+def test_reference_style_module_variants(n_bits, block_size, symmetric, qa):
+  # :182-286 -- int4 per-channel, blockwise, asymmetric per-channel (with and without act-quant), asymmetric blockwise
+  from xla_b200 import weight_prep as wp
+  torch.manual_seed(123456)
+  lin = torch.nn.Linear(6, 8, bias=False)
+  x = torch.randn(3, 6)
+  out_fp = lin(x)
+  m = wp.quantize_linear(lin, n_bits=n_bits, block_size=block_size, symmetric=symmetric, quantize_activation=qa).to(DEV)
+  out_q = m(x.to(DEV))
+  assert _cos(out_fp, out_q) > (0.99 if n_bits == 8 else 0.95)
+  # and against the oracle on the same quantized tensors
+  ref = qo.quantized_matmul(x, m.weight.cpu(), m.weight_scaler.cpu(), None if m.zero_point is None else m.zero_point.cpu(),
+                            block_size=block_size, quantize_activation=qa)
+  assert qo.max_abs_rel(out_q, ref) < 1e-4
+
+
+def test_torch_compile_and_cuda_graph_pass_through():
+  # the op is an opaque custom op with a Meta kernel: Dynamo traces it, a CUDA graph captures it (:128-143)
+  g = qc.gen(30)
+  x = cu(qc.activations(g, 4, 1024))
+  w = cu(qc.int8_weight(g, 512, 1024))
+  s = cu(qc.per_channel_scale(g, 512))
+  m = xla_b200.XlaQuantizedLinear(1024, 512, is_symmetric=True)
+  m.load_quantized_weight(w, s)
+  eager = m(x)
+  compiled = torch.compile(m, backend="aot_eager", fullgraph=True)
+  assert torch.equal(compiled(x), eager)
+  st = torch.cuda.Stream()
+  with torch.cuda.stream(st):
+    m(x)
+    st.synchronize()
+    gr = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gr, stream=st):
+      y = m(x)
+    gr.replay()
+    st.synchronize()
+  assert torch.equal(y, eager)

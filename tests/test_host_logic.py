@@ -107,3 +107,33 @@ def test_variant_heuristic_is_shape_only():
   assert L.qmm_variant_for(xla_b200._capi.OP_W4A16_BLOCKWISE_PACKED, 1, 14336, 4096, 128, 0) == b"mma"
   assert L.qmm_variant_for(xla_b200._capi.OP_W4A16_BLOCKWISE_PACKED, 64, 14336, 4096, 128, 0) == b"tcgen05"
   assert L.qmm_variant_for(xla_b200._capi.OP_W8A8_PERCHANNEL, 2048, 4096, 4096, 0, 0) == b"tcgen05"
+
+
+def test_rtn_quantizer_layouts_and_reconstruction():
+  """quantize_rtn reproduces the reference test helper's layouts (test_quantized_matmul.py:25-74)."""
+  from xla_b200 import weight_prep as wp
+  g = torch.Generator().manual_seed(0)
+  w = torch.randn(8, 12, generator=g)
+  q, s, zp = wp.quantize_rtn(w, n_bits=8)
+  assert q.dtype == torch.int8 and q.shape == (8, 12) and s.shape == (8,) and zp is None
+  assert (q.float() * s[:, None] - w).abs().max() <= s.max() * 0.51
+  q, s, zp = wp.quantize_rtn(w, n_bits=4, block_size=4, symmetric=False)
+  assert q.shape == (3, 4, 8) and s.shape == (3, 8) and zp.shape == (3, 8)
+  assert int(q.min()) >= -8 and int(q.max()) <= 7
+  # dequantise: w[n, b*bs+c] ~ q[b,c,n]*s[b,n] - zp[b,n]   (zp is in scaled units)
+  w_dq = (q.float() * s[:, None, :] - zp[:, None, :]).permute(2, 0, 1).reshape(8, 12)
+  assert (w_dq - w).abs().max() <= s.max() * 0.51
+  lin = torch.nn.Linear(12, 8, bias=False)
+  m = wp.quantize_linear(lin, n_bits=8, block_size=4)
+  assert tuple(m.weight.shape) == (3, 4, 8) and m.block_size == 4 and m.zero_point is None
+
+  class Net(torch.nn.Module):
+
+    def __init__(self):
+      super().__init__()
+      self.a = torch.nn.Linear(12, 8, bias=False)
+      self.b = torch.nn.Sequential(torch.nn.Linear(8, 8, bias=True), torch.nn.Linear(8, 4, bias=False))
+
+  net = wp.swap_linears(Net(), n_bits=8)
+  assert isinstance(net.a, xla_b200.XlaQuantizedLinear) and isinstance(net.b[1], xla_b200.XlaQuantizedLinear)
+  assert isinstance(net.b[0], torch.nn.Linear)  # has a bias: left alone
