@@ -482,6 +482,20 @@ def test_mma_w8a16_per_channel(M, xdtype):
     op(cu(qc.activations(g, 33, K, dtype=xdtype)), cu(w), cu(s), variant="mma")
 
 
+@pytest.mark.parametrize("N", [148 * 16 * 2 + 5, 148 * 16 * 3 + 40, 20000])
+def test_mma_staged_tile_slots_and_rounds(N):
+  """9..32 tokens: the per-SM kernel with 2, 4 and 8 row tiles per CTA, and more than one round of tiles."""
+  g = qc.gen(22)
+  K, bs, M = 1024, 128, 20
+  x = qc.activations(g, M, K)
+  w_nk = qc.int4_weight(g, N, K)
+  wp = xla_b200.pack_int4(cu(w_nk))
+  s = qc.blockwise_scale(g, K // bs, N)
+  exact = qo.quantized_matmul(x.float(), qc.to_sbn(w_nk, bs), s, block_size=bs, dot_round=None)
+  out = packed_op(cu(x), wp, cu(s), block_size=bs, int4_weight=True, weight_is_packed=True, variant="mma")
+  assert qo.max_abs_rel(out, exact) < TOL_F32
+
+
 # ---------------------------------------------------------------------------------------------
 # the reference's module-level tests, replayed on the GPU (test/quantized_ops/test_quantized_matmul.py)
 # ---------------------------------------------------------------------------------------------

@@ -18,6 +18,8 @@
 // every fold with bias * sum_k x, which an extra MMA against an all-ones operand supplies.
 //
 // Semantics: torch_xla/experimental/xla_quantized_matmul.py:152-159 (per channel), :165-170 (blockwise).
+#include <algorithm>
+#include <cstdlib>
 #include <type_traits>
 
 #include "common.cuh"
@@ -91,6 +93,18 @@ __device__ __forceinline__ void cvt_s8x4_biased(uint32_t w, uint32_t* p) {
   }
 }
 
+// packed pair minus (bias, bias): exact, the operands are small integers
+template <typename XT>
+__device__ __forceinline__ uint32_t sub_bias(uint32_t p, float bias) {
+  if constexpr (std::is_same<XT, __half>::value) {
+    const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&p), __float2half2_rn(bias));
+    return *reinterpret_cast<const uint32_t*>(&r);
+  } else {
+    const __nv_bfloat162 r = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&p), __float2bfloat162_rn(bias));
+    return *reinterpret_cast<const uint32_t*>(&r);
+  }
+}
+
 // NT = number of 8-token tiles (M <= 8*NT); RG = 16-row groups per CTA (each warp converts RG groups per
 // step and reuses its activation registers for all of them); WARPS = warps splitting K.
 // One "fold" = the end of a scale block (blockwise) or of a single step (per-channel): the partial tile,
@@ -104,8 +118,12 @@ __global__ void __launch_bounds__(WARPS * 32)
   constexpr int VPL = VPS / 4;          // values per lane per row per step: 32 or 16
   constexpr int XREGS = VPL / 2;        // packed activation pairs per lane per token tile: 16 or 8
   constexpr int ROWS = 16 * RG;         // output rows per CTA
+  // With one token tile the bias stays in and a ones-MMA removes it (the integer pipe is the limiter
+  // there); with more tiles the tensor pipe matters more, so the bias is subtracted in the conversion
+  // (a packed subtract on the otherwise idle FMA pipe) and the extra MMAs disappear.
   constexpr float kBias = Bias<XT, WBITS>::value;
-  constexpr bool kHasBias = kBias != 0.f;
+  constexpr bool kHasBias = kBias != 0.f && NT == 1;
+  constexpr bool kSubBias = kBias != 0.f && NT != 1;
   constexpr uint32_t kOnes = Bias<XT, WBITS>::ones;
   __shared__ float s_part[WARPS][ROWS][NT * 8];
 
@@ -220,6 +238,13 @@ __global__ void __launch_bounds__(WARPS * 32)
           uint32_t pa[4], pb[4];
           cvt_s4x8_biased<XT>(reinterpret_cast<const uint32_t*>(&wc[2 * r])[wi], pa);
           cvt_s4x8_biased<XT>(reinterpret_cast<const uint32_t*>(&wc[2 * r + 1])[wi], pb);
+          if constexpr (kSubBias) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              pa[q] = sub_bias<XT>(pa[q], kBias);
+              pb[q] = sub_bias<XT>(pb[q], kBias);
+            }
+          }
           const uint32_t a_lo[4] = {pa[0], pb[0], pa[1], pb[1]};
           const uint32_t a_hi[4] = {pa[2], pb[2], pa[3], pb[3]};
 #pragma unroll
@@ -228,10 +253,12 @@ __global__ void __launch_bounds__(WARPS * 32)
             mma_16816<XT>(part[r][i], a_hi, xr[i][4 * wi + 2], xr[i][4 * wi + 3]);
           }
         }
+        if constexpr (kHasBias) {
 #pragma unroll
-        for (int i = 0; i < NT; ++i) {
-          mma_16816<XT>(xsum[i], ones, xr[i][4 * wi], xr[i][4 * wi + 1]);
-          mma_16816<XT>(xsum[i], ones, xr[i][4 * wi + 2], xr[i][4 * wi + 3]);
+          for (int i = 0; i < NT; ++i) {
+            mma_16816<XT>(xsum[i], ones, xr[i][4 * wi], xr[i][4 * wi + 1]);
+            mma_16816<XT>(xsum[i], ones, xr[i][4 * wi + 2], xr[i][4 * wi + 3]);
+          }
         }
       } else {
 #pragma unroll
@@ -239,6 +266,13 @@ __global__ void __launch_bounds__(WARPS * 32)
           uint32_t pa[2], pb[2];
           cvt_s8x4_biased<XT>(reinterpret_cast<const uint32_t*>(&wc[2 * r])[wi], pa);
           cvt_s8x4_biased<XT>(reinterpret_cast<const uint32_t*>(&wc[2 * r + 1])[wi], pb);
+          if constexpr (kSubBias) {
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              pa[q] = sub_bias<XT>(pa[q], kBias);
+              pb[q] = sub_bias<XT>(pb[q], kBias);
+            }
+          }
           const uint32_t a[4] = {pa[0], pb[0], pa[1], pb[1]};
 #pragma unroll
           for (int i = 0; i < NT; ++i) mma_16816<XT>(part[r][i], a, xr[i][2 * wi], xr[i][2 * wi + 1]);
@@ -296,14 +330,293 @@ __global__ void __launch_bounds__(WARPS * 32)
   }
 }
 
+// ---- token batches of 9..32 ----------------------------------------------------------------------------
+//
+// With more than one token tile the activations (M*K*2 bytes: 256 KB for 32 tokens of 4096) no longer
+// stay in L1, and the kernel above re-reads them from L2 once per CTA: 448 CTAs x 256 KB is four times
+// the weight stream.  This kernel runs one 16-warp CTA per SM instead.  The CTA owns up to TR row tiles
+// (16 output rows each) at a time, WK = 16/TR warps share the K steps of one tile, and all of them read
+// the activations from a shared-memory ring that the whole CTA fills with cp.async, one chunk of 8 steps
+// at a time: the activations cross L2 -> SM once per CTA and round.  Weights still go HBM -> registers,
+// two steps ahead of their use.
+//
+// Shared-memory layout of a chunk: one row per token, 16-byte units of the row permuted by
+// u ^ (((u >> 3) & 1) << 1) and rows pitched by one extra unit; with that the 16-byte fragment reads of
+// a quarter warp (two tokens x four k spans) spread over all 32 banks.
+constexpr int kStagedWarps = 16;
+constexpr int kChunkSteps = 8;
+
+__device__ __forceinline__ int swz_unit(int u) { return u ^ (((u >> 3) & 1) << 1); }
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+
+// same MMA as mma_16816 but not volatile: the compiler may interleave independent accumulator chains
+template <typename XT>
+__device__ __forceinline__ void mma_16816_nv(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  if constexpr (std::is_same<XT, __half>::value) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  } else {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+}
+
+struct StagedStep {  // one K step of a warp in flight: 16 bytes of two weight rows and their block scales
+  uint4 w[2];
+  float sc[2];
+};
+
+template <int WBITS, typename XT, int NT>
+__global__ void __launch_bounds__(kStagedWarps * 32, 1)
+    decode_mma_staged_kernel(const XT* __restrict__ x, const uint8_t* __restrict__ w, const float* __restrict__ scale,
+                             void* __restrict__ out, int out_dt, int M, int N, int K, int steps_per_block,
+                             int spb_shift, int blockwise, int tiles, int TR, int WK, int rounds) {
+  constexpr int VPS = 512 / WBITS;            // weight values per row per step
+  constexpr int UPS = VPS * 2 / 16;           // 16-byte activation units per token per step: 16 or 8
+  constexpr int UPL = UPS / 4;                // units per lane per step: 4 or 2
+  constexpr int ROWS_X = NT * 8;              // token rows held in shared memory
+  constexpr int CHUNK_UNITS = kChunkSteps * UPS;
+  constexpr int PITCH = CHUNK_UNITS * 16 + 16;
+  constexpr int STAGE_BYTES = ROWS_X * PITCH;
+  constexpr int THREADS = kStagedWarps * 32;
+  constexpr float kBias = Bias<XT, WBITS>::value;
+  constexpr int kRedPitch = 17;
+  static_assert(kStagedWarps * kRedPitch * ROWS_X * 4 <= 2 * STAGE_BYTES, "the reduction buffer reuses the ring");
+  extern __shared__ __align__(16) unsigned char smem[];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int ts = warp / WK, wk = warp - ts * WK;   // tile slot of this warp and its share of the K steps
+  const int64_t pitch = (int64_t)K * WBITS / 8;
+  const int steps = K / VPS;
+  const int nchunks = (steps + kChunkSteps - 1) / kChunkSteps;
+  // a step of this warp ends a scale block when the warp's next step lies in another block; with a
+  // stride of WK steps that is every step once WK is a multiple of the block length
+  const bool fold_every = blockwise && (WK % steps_per_block == 0);
+  // fragment reads: byte offset of this lane's first unit inside a step, and the swizzle it sees (the
+  // swizzle bit of unit 16*cs + 4*t + q, or 8*cs + 2*t + q, does not depend on q or on the step pair)
+  const int lane_unit = t * UPL;
+
+  // cp.async of chunk c into ring slot c & 1 (tokens beyond M are zero-filled)
+  const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
+  auto issue_chunk = [&](int c) {
+    const int units_here = min(kChunkSteps, steps - c * kChunkSteps) * UPS;
+    const uint32_t dst0 = smem_base + (uint32_t)(c & 1) * STAGE_BYTES;
+    const XT* src0 = x + (int64_t)c * (kChunkSteps * VPS);
+#pragma unroll
+    for (int it = 0; it < ROWS_X * CHUNK_UNITS / THREADS; ++it) {
+      const int idx = tid + it * THREADS;
+      const int row = idx / CHUNK_UNITS, u = idx - row * CHUNK_UNITS;
+      if (u < units_here) {
+        const bool ok = row < M;
+        cp_async_16(dst0 + row * PITCH + swz_unit(u) * 16, src0 + (int64_t)(ok ? row : 0) * K + u * 8, ok ? 16 : 0);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  static_assert((ROWS_X * CHUNK_UNITS) % THREADS == 0, "whole copies per thread");
+
+  bool first = true;
+  for (int round = 0; round < rounds; ++round) {
+    const int tile = blockIdx.x + (round * TR + ts) * gridDim.x;
+    const bool active = ts < TR && tile < tiles;
+    const uint8_t* wrow[2];
+    const float* srow[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      int n = (active ? tile : 0) * 16 + g + 8 * r;
+      if (n >= N) n = N - 1;
+      wrow[r] = w + n * pitch + 16 * t;
+      srow[r] = scale + n;
+    }
+    auto folds = [&](int s) {
+      if (fold_every) return true;
+      const int sn = s + WK;
+      if (sn >= steps) return true;
+      if (!blockwise) return false;
+      const int b = spb_shift >= 0 ? (s >> spb_shift) : (s / steps_per_block);
+      const int bn = spb_shift >= 0 ? (sn >> spb_shift) : (sn / steps_per_block);
+      return bn != b;
+    };
+    auto fetch = [&](int s, StagedStep& d) {
+      if (active && s < steps) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) d.w[r] = ld_stream_u4(wrow[r] + s * 64);
+        if (blockwise && folds(s)) {
+          const int b = spb_shift >= 0 ? (s >> spb_shift) : (s / steps_per_block);
+#pragma unroll
+          for (int r = 0; r < 2; ++r) d.sc[r] = __ldg(srow[r] + (int64_t)b * N);
+        }
+      }
+    };
+    StagedStep qa, qb;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      qa.w[r] = qb.w[r] = make_uint4(0, 0, 0, 0);
+      qa.sc[r] = qb.sc[r] = 1.f;
+    }
+    fetch(wk, qa);
+    fetch(wk + WK, qb);
+    if (first) {
+      // weights are static: their first loads may overlap the previous kernel of the stream; the
+      // activations and every store of this kernel come after the wait
+      asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      first = false;
+    }
+    issue_chunk(0);
+    if (nchunks > 1) issue_chunk(1);
+
+    float total[NT][4], part[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) total[i][j] = part[i][j] = 0.f;
+
+    // one K step: convert q's weights, multiply with the chunk's activations, fold, refill q two steps ahead
+    auto do_step = [&](int s, int c, StagedStep& q) {
+      const uint4 w0 = q.w[0], w1 = q.w[1];
+      const float sc0 = q.sc[0], sc1 = q.sc[1];
+      fetch(s + 2 * WK, q);
+      const int u0 = (s - c * kChunkSteps) * UPS + lane_unit;
+      const unsigned char* xb = smem + (c & 1) * STAGE_BYTES + g * PITCH;
+      if constexpr (WBITS == 4) {
+        const int sw = ((u0 >> 3) & 1) << 1;
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) {
+          uint32_t pa[4], pb[4];
+          cvt_s4x8_biased<XT>(reinterpret_cast<const uint32_t*>(&w0)[wi], pa);
+          cvt_s4x8_biased<XT>(reinterpret_cast<const uint32_t*>(&w1)[wi], pb);
+#pragma unroll
+          for (int qd = 0; qd < 4; ++qd) {
+            pa[qd] = sub_bias<XT>(pa[qd], kBias);
+            pb[qd] = sub_bias<XT>(pb[qd], kBias);
+          }
+          const uint32_t a_lo[4] = {pa[0], pb[0], pa[1], pb[1]};
+          const uint32_t a_hi[4] = {pa[2], pb[2], pa[3], pb[3]};
+          const unsigned char* xp = xb + ((u0 + wi) ^ sw) * 16;
+          uint4 xv[NT];
+#pragma unroll
+          for (int i = 0; i < NT; ++i) xv[i] = *reinterpret_cast<const uint4*>(xp + i * 8 * PITCH);
+#pragma unroll
+          for (int i = 0; i < NT; ++i) mma_16816_nv<XT>(part[i], a_lo, xv[i].x, xv[i].y);
+#pragma unroll
+          for (int i = 0; i < NT; ++i) mma_16816_nv<XT>(part[i], a_hi, xv[i].z, xv[i].w);
+        }
+      } else {
+        const int sw = ((u0 >> 3) & 1) << 1;
+#pragma unroll
+        for (int wp = 0; wp < 2; ++wp) {  // two weight words share one 16-byte activation unit
+          uint32_t a[2][4];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t pa[2], pb[2];
+            cvt_s8x4_biased<XT>(reinterpret_cast<const uint32_t*>(&w0)[2 * wp + h], pa);
+            cvt_s8x4_biased<XT>(reinterpret_cast<const uint32_t*>(&w1)[2 * wp + h], pb);
+            if constexpr (kBias != 0.f) {
+#pragma unroll
+              for (int qd = 0; qd < 2; ++qd) {
+                pa[qd] = sub_bias<XT>(pa[qd], kBias);
+                pb[qd] = sub_bias<XT>(pb[qd], kBias);
+              }
+            }
+            a[h][0] = pa[0];
+            a[h][1] = pb[0];
+            a[h][2] = pa[1];
+            a[h][3] = pb[1];
+          }
+          const unsigned char* xp = xb + ((u0 + wp) ^ sw) * 16;
+          uint4 xv[NT];
+#pragma unroll
+          for (int i = 0; i < NT; ++i) xv[i] = *reinterpret_cast<const uint4*>(xp + i * 8 * PITCH);
+#pragma unroll
+          for (int i = 0; i < NT; ++i) mma_16816_nv<XT>(part[i], a[0], xv[i].x, xv[i].y);
+#pragma unroll
+          for (int i = 0; i < NT; ++i) mma_16816_nv<XT>(part[i], a[1], xv[i].z, xv[i].w);
+        }
+      }
+      if (folds(s)) {
+#pragma unroll
+        for (int i = 0; i < NT; ++i) {
+          total[i][0] = fmaf(sc0, part[i][0], total[i][0]);
+          total[i][1] = fmaf(sc0, part[i][1], total[i][1]);
+          total[i][2] = fmaf(sc1, part[i][2], total[i][2]);
+          total[i][3] = fmaf(sc1, part[i][3], total[i][3]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) part[i][j] = 0.f;
+        }
+      }
+    };
+
+    int s = wk;
+    for (int c = 0; c < nchunks; ++c) {
+      if (c + 1 < nchunks)
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+      else
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+      __syncthreads();
+      const int s_end = min((c + 1) * kChunkSteps, steps);
+      if (active) {
+        // steps alternate between the two in-flight slots; pairs keep the slot names static
+        for (; s + WK < s_end; s += 2 * WK) {
+          do_step(s, c, qa);
+          do_step(s + WK, c, qb);
+        }
+        if (s < s_end) {  // odd count in this chunk: run one step and swap the slots
+          do_step(s, c, qa);
+          s += WK;
+          const StagedStep tmp = qa;
+          qa = qb;
+          qb = tmp;
+        }
+      }
+      __syncthreads();  // every warp is done with ring slot c & 1
+      if (c + 2 < nchunks) issue_chunk(c + 2);
+    }
+
+    // cross-warp reduction through the (now idle) ring, then the store
+    float* red = reinterpret_cast<float*>(smem);
+    if (active) {
+#pragma unroll
+      for (int i = 0; i < NT; ++i) {
+        // token-major with a pitch of 17 floats: rows g, g+8 of tokens 2t, 2t+1 land on distinct banks
+        float* r0 = red + (warp * ROWS_X + 8 * i + 2 * t) * kRedPitch + g;
+        r0[0] = total[i][0];
+        r0[kRedPitch] = total[i][1];
+        r0[8] = total[i][2];
+        r0[kRedPitch + 8] = total[i][3];
+      }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < TR * 16 * ROWS_X; idx += THREADS) {
+      const int slot = idx / (16 * ROWS_X), rem = idx - slot * (16 * ROWS_X);
+      const int row = rem & 15, tok = rem >> 4;  // consecutive threads -> consecutive n
+      const int otile = blockIdx.x + (round * TR + slot) * gridDim.x;
+      const int n = otile * 16 + row;
+      if (otile < tiles && n < N && tok < M) {
+        float v = 0.f;
+        for (int j = 0; j < WK; ++j) v += red[((slot * WK + j) * ROWS_X + tok) * kRedPitch + row];
+        if (!blockwise) v *= __ldg(scale + n);
+        store_from_f32(out, (int64_t)tok * N + n, out_dt, v);
+      }
+    }
+    __syncthreads();  // the ring is refilled next round
+  }
+}
+
 // Launch with programmatic stream serialization: this kernel may be scheduled while the previous
 // kernel of the stream drains, and parks at its griddepcontrol.wait until that kernel has finished.
 template <typename Kernel, typename... Args>
-cudaError_t launch_pdl(Kernel kern, unsigned grid, unsigned block, cudaStream_t st, Args... args) {
+cudaError_t launch_pdl(Kernel kern, unsigned grid, unsigned block, size_t smem_bytes, cudaStream_t st, Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(block);
-  cfg.dynamicSmemBytes = 0;
+  cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -311,6 +624,35 @@ cudaError_t launch_pdl(Kernel kern, unsigned grid, unsigned block, cudaStream_t 
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
+template <int WBITS, typename XT, int NT>
+cudaError_t launch_staged(const XT* xp, const uint8_t* wp, const float* scale, void* out, int out_dt, int64_t M,
+                          int64_t N, int64_t K, int spb, int shift, int bw, cudaStream_t st) {
+  constexpr int VPS = 512 / WBITS;
+  constexpr int PITCH = kChunkSteps * (VPS * 2 / 16) * 16 + 16;
+  constexpr size_t kSmem = 2 * (size_t)(NT * 8) * PITCH;
+  auto kern = decode_mma_staged_kernel<WBITS, XT, NT>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  } else if (dev >= 64) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem);
+    if (e != cudaSuccess) return e;
+  }
+  const int tiles = (int)ceil_div(N, 16);
+  const int grid = (int)std::min<int64_t>(sm_count(), tiles);
+  const int per_cta = (int)ceil_div(tiles, grid);
+  int tr = 1;
+  while (tr < per_cta && tr < 8) tr *= 2;          // row tiles a CTA works on at a time
+  const int wk = std::min(kStagedWarps / tr, 8);   // warps sharing the K steps of one tile
+  const int rounds = (int)ceil_div(per_cta, tr);
+  return launch_pdl(kern, (unsigned)grid, kStagedWarps * 32, kSmem, st, xp, wp, scale, out, out_dt, (int)M, (int)N, (int)K, spb,
+                    shift, bw, tiles, tr, wk, rounds);
 }
 
 template <int WBITS, typename XT>
@@ -327,18 +669,17 @@ int launch_nt(const void* x, const void* w, const float* scale, void* out, int o
   const XT* xp = reinterpret_cast<const XT*>(x);
   const uint8_t* wp = reinterpret_cast<const uint8_t*>(w);
 #define QMM_DECODE_LAUNCH(NT, RG, WARPS)                                                                        \
-  launch_pdl(decode_mma_kernel<WBITS, XT, NT, RG, WARPS>, (unsigned)ceil_div(N, 16 * RG), WARPS * 32, st, xp, wp, \
+  launch_pdl(decode_mma_kernel<WBITS, XT, NT, RG, WARPS>, (unsigned)ceil_div(N, 16 * RG), WARPS * 32, 0, st, xp, wp, \
              scale, out, out_dt, (int)M, N, K, spb, shift, bw)
-  // measured on B200 (w [14336,4096] int4): 16 rows per CTA is best for one token tile; with two or four
-  // tiles the activation traffic through L1 dominates and 32 rows per CTA (activation registers reused
-  // for two row groups) wins
+  // one token tile: many small CTAs, activations through L1 (64 KB for 8 tokens of 4096);
+  // two or four tiles: one CTA per SM with the activations staged in shared memory
   cudaError_t err;
   if (M <= 8)
     err = QMM_DECODE_LAUNCH(1, 1, 4);
   else if (M <= 16)
-    err = QMM_DECODE_LAUNCH(2, 2, 4);
+    err = launch_staged<WBITS, XT, 2>(xp, wp, scale, out, out_dt, M, N, K, spb, shift, bw, st);
   else
-    err = QMM_DECODE_LAUNCH(4, 2, 4);
+    err = launch_staged<WBITS, XT, 4>(xp, wp, scale, out, out_dt, M, N, K, spb, shift, bw, st);
   if (err != cudaSuccess) {
     cudaGetLastError();
     return fail(QMM_ERR_LAUNCH, "decode_mma_kernel launch: %s", cudaGetErrorString(err));
@@ -358,7 +699,7 @@ bool decode_mma_supported(int wbits, int64_t M, int64_t N, int64_t K, int64_t bl
   if (K % vps != 0) return false;                                 // whole 64-byte steps per weight row
   if (block_size > 0 && block_size % vps != 0) return false;      // a step stays inside one scale block
   if (!aligned(x, 16) || !aligned(w, 16)) return false;
-  if (ceil_div(N, 16) > 2147483647LL) return false;
+  if (N > 2147483647LL - 16 || K > 2147483647LL) return false;    // 32-bit row and step indices
   return true;
 }
 
