@@ -60,6 +60,7 @@ typedef enum qmm_variant {
   QMM_VARIANT_GEMV = 2,    /* decode: warp-per-row, 128-bit weight loads, M <= 8 */
   QMM_VARIANT_TCGEN05 = 3, /* TMA -> shared memory -> tcgen05.mma with TMEM accumulators */
   QMM_VARIANT_MMA = 4,     /* decode: weights dequantised in registers into warp-level MMAs, M <= 32 */
+  QMM_VARIANT_TMEM = 5,    /* decode: weights dequantised in registers into tensor memory, tcgen05.mma, M <= 32 */
 } qmm_variant;
 
 typedef enum qmm_op {

@@ -11,10 +11,10 @@ import torch
 from . import _build
 
 F32, BF16, F16 = 0, 1, 2
-AUTO, GENERIC, GEMV, TCGEN05, MMA = 0, 1, 2, 3, 4
+AUTO, GENERIC, GEMV, TCGEN05, MMA, TMEM = 0, 1, 2, 3, 4, 5
 OP_W8A16_PERCHANNEL, OP_BLOCKWISE_SBN, OP_W4A16_BLOCKWISE_PACKED, OP_W8A8_PERCHANNEL, OP_W4A16_PERCHANNEL_PACKED = range(5)
 
-VARIANTS = {"auto": AUTO, "generic": GENERIC, "gemv": GEMV, "tcgen05": TCGEN05, "mma": MMA}
+VARIANTS = {"auto": AUTO, "generic": GENERIC, "gemv": GEMV, "tcgen05": TCGEN05, "mma": MMA, "tmem": TMEM}
 
 _DTYPES = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
 

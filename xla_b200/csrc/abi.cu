@@ -206,6 +206,10 @@ int qmm_w8a16_perchannel(const void* x, int x_dtype, const int8_t* w, const floa
       log_choice("w8a16_perchannel", "mma", M, N, K);
       if (zp) return fail(QMM_ERR_UNSUPPORTED, "the register-dequant decode kernel does not take a zero point");
       return launch_decode_mma(8, x, x_dtype, w, scale, out, out_dtype, M, N, K, 0, st);
+    case QMM_VARIANT_TMEM:
+      log_choice("w8a16_perchannel", "tmem", M, N, K);
+      if (zp) return fail(QMM_ERR_UNSUPPORTED, "w8a16_perchannel: the tensor-memory decode kernel takes no zero point");
+      return launch_decode_tc(8, x, x_dtype, w, scale, out, out_dtype, M, N, K, 0, st);
     case QMM_VARIANT_TCGEN05:
       log_choice("w8a16_perchannel", "tcgen05", M, N, K);
       if (zp) return fail(QMM_ERR_UNSUPPORTED, "tcgen05 weight-only kernel does not take a zero point");
@@ -262,6 +266,10 @@ int qmm_w4a16_blockwise_packed(const void* x, int x_dtype, const uint8_t* wp, co
       log_choice("w4a16_blockwise_packed", "mma", M, N, K);
       if (zp) return fail(QMM_ERR_UNSUPPORTED, "the register-dequant decode kernel does not take a zero point");
       return launch_decode_mma(4, x, x_dtype, wp, scale, out, out_dtype, M, N, K, block_size, st);
+    case QMM_VARIANT_TMEM:
+      log_choice("w4a16_blockwise_packed", "tmem", M, N, K);
+      if (zp) return fail(QMM_ERR_UNSUPPORTED, "w4a16_blockwise_packed: the tensor-memory decode kernel takes no zero point");
+      return launch_decode_tc(4, x, x_dtype, wp, scale, out, out_dtype, M, N, K, block_size, st);
     case QMM_VARIANT_TCGEN05:
       log_choice("w4a16_blockwise_packed", "tcgen05", M, N, K);
       if (zp) return fail(QMM_ERR_UNSUPPORTED, "tcgen05 weight-only kernel does not take a zero point");
@@ -291,6 +299,10 @@ int qmm_w4a16_perchannel_packed(const void* x, int x_dtype, const uint8_t* wp, c
       log_choice("w4a16_perchannel_packed", "mma", M, N, K);
       if (zp) return fail(QMM_ERR_UNSUPPORTED, "the register-dequant decode kernel does not take a zero point");
       return launch_decode_mma(4, x, x_dtype, wp, scale, out, out_dtype, M, N, K, 0, st);
+    case QMM_VARIANT_TMEM:
+      log_choice("w4a16_perchannel_packed", "tmem", M, N, K);
+      if (zp) return fail(QMM_ERR_UNSUPPORTED, "w4a16_perchannel_packed: the tensor-memory decode kernel takes no zero point");
+      return launch_decode_tc(4, x, x_dtype, wp, scale, out, out_dtype, M, N, K, 0, st);
     case QMM_VARIANT_TCGEN05:
       log_choice("w4a16_perchannel_packed", "tcgen05", M, N, K);
       if (zp) return fail(QMM_ERR_UNSUPPORTED, "tcgen05 weight-only kernel does not take a zero point");

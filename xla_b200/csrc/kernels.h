@@ -50,6 +50,14 @@ bool decode_mma_supported(int wbits, int64_t M, int64_t N, int64_t K, int64_t bl
 int launch_decode_mma(int wbits, const void* x, int x_dt, const void* w, const float* scale, void* out, int out_dt,
                       int64_t M, int64_t N, int64_t K, int64_t block_size, cudaStream_t st);
 
+// ---- decode_tc.cu -------------------------------------------------------------------------
+// Decode kernel on tcgen05 with the weight operand written to tensor memory (M <= 32, bf16/f16
+// activations, no zero point), K split over a thread-block cluster.
+bool decode_tc_supported(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size, const void* x, int x_dt,
+                         const void* w, bool has_zp);
+int launch_decode_tc(int wbits, const void* x, int x_dt, const void* w, const float* scale, void* out, int out_dt,
+                     int64_t M, int64_t N, int64_t K, int64_t block_size, cudaStream_t st);
+
 // ---- act_quant.cu -------------------------------------------------------------------------
 int launch_quantize_activation(const void* x, int x_dt, int8_t* xq, float* x_scale,
                                int32_t* rowsum, int64_t M, int64_t K, int saturate,
