@@ -422,14 +422,48 @@ def run_ours(args, rank, world, local_rank):
     hx = {m: torch.randn(m, wl.K).bfloat16().pin_memory() for m in wl.MS}
     hy = {m: torch.empty(m, wl.N, dtype=torch.bfloat16).pin_memory() for m in wl.MS}
     e2e_reps = max(1, min(reps, 8))
+    # Host copies run on two side streams so that the copy-in of call i+1 and the copy-out of call i-1
+    # overlap the kernel of call i; hand-offs are events.  The copies and events are issued through the
+    # CUDA runtime bindings with an explicit stream (switching torch's current stream per call costs more
+    # host time than the kernel takes); the operator itself is called exactly as a user calls it.
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    xin = {m: [torch.empty(m, wl.K, dtype=torch.bfloat16, device=dev) for _ in range(e2e_reps)] for m in wl.MS}
+    try:
+      from cuda.bindings import runtime as rt
+      ev_in = [rt.cudaEventCreateWithFlags(rt.cudaEventDisableTiming)[1] for _ in range(e2e_reps)]
+      ev_k = [rt.cudaEventCreateWithFlags(rt.cudaEventDisableTiming)[1] for _ in range(e2e_reps)]
+      H2D, D2H = rt.cudaMemcpyKind.cudaMemcpyHostToDevice, rt.cudaMemcpyKind.cudaMemcpyDeviceToHost
+    except Exception as exc:  # bindings absent: plain in-order copies on the compute stream
+      print(f"[bench] CUDA runtime bindings unavailable ({exc}); end-to-end copies stay on the compute stream",
+            file=sys.stderr)
+      rt = None
+    h_in, h_c, h_out = s_in.cuda_stream, stream.cuda_stream, s_out.cuda_stream
 
     def e2e_step():
+      keep = []
       for m in wl.MS:
-        for _ in range(e2e_reps):
-          xd = hx[m].to(dev, non_blocking=True)
+        if rt is None:
+          for _ in range(e2e_reps):
+            xd = hx[m].to(dev, non_blocking=True)
+            y = wl.launch(m, xd)
+            hy[m].copy_(y, non_blocking=True)
+          continue
+        nin, nout = 2 * m * wl.K, 2 * m * wl.N
+        src, dst = hx[m].data_ptr(), hy[m].data_ptr()
+        for i in range(e2e_reps):
+          xd = xin[m][i]  # one staging buffer per call of the step: no reuse before the final synchronize
+          rt.cudaMemcpyAsync(xd.data_ptr(), src, nin, H2D, h_in)
+          rt.cudaEventRecord(ev_in[i], h_in)
+          rt.cudaStreamWaitEvent(h_c, ev_in[i], 0)
           y = wl.launch(m, xd)
-          hy[m].copy_(y, non_blocking=True)
+          rt.cudaEventRecord(ev_k[i], h_c)
+          rt.cudaStreamWaitEvent(h_out, ev_k[i], 0)
+          rt.cudaMemcpyAsync(dst, y.data_ptr(), nout, D2H, h_out)
+          keep.append(y)  # alive until the copy-out stream has been synchronised
+        # the next batch size reuses the events: its copies are ordered behind these on the same streams
+      s_in.synchronize()
       stream.synchronize()
+      s_out.synchronize()
 
     for _ in range(max(3, args.warmup)):
       e2e_step()

@@ -75,11 +75,27 @@ def dtype_code(dt):
 
 
 def ptr(t):
-  return None if t is None else ctypes.c_void_p(t.data_ptr())
+  """Device address as a plain int (ctypes converts it for a void* parameter); None stays None."""
+  return None if t is None else t.data_ptr()
+
+
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
 def stream_ptr(device=None):
-  return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+  """Handle of torch's current stream on `device` (an int usable as cudaStream_t)."""
+  if _raw_stream is not None:
+    idx = torch.cuda.current_device() if device is None or device.index is None else device.index
+    return _raw_stream(idx)
+  return torch.cuda.current_stream(device).cuda_stream
+
+
+def on_device(device, fn):
+  """Runs fn() with `device` current; skips the context switch when it already is."""
+  if device.index is None or device.index == torch.cuda.current_device():
+    return fn()
+  with torch.cuda.device(device):
+    return fn()
 
 
 def check(status):

@@ -106,29 +106,32 @@ def quantized_matmul_packed(x, w, scaler, zero_point=None, block_size=-1, int4_w
   s32, zp32 = _qm._f32(scaler), _qm._f32(zero_point)
   L = _capi.lib()
   variant = _capi.VARIANTS[_qm._variant]
-  with torch.cuda.device(x.device):
-    st = _capi.stream_ptr(x.device)
+
+  def run():
     if quantize_activation:
       if weight_is_packed:
         raise NotImplementedError("W4A8 (packed int4 weights with activation quantization) is not supported")
-      out = _qm._w8a8(x2, w, s32, zp32, out_dtype)
-    else:
-      out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-      args = (_capi.ptr(x2), _capi.dtype_code(x2.dtype), _capi.ptr(w), _capi.ptr(s32), _capi.ptr(zp32),
-              _capi.ptr(out), _capi.dtype_code(out_dtype), M, N, K)
-      if weight_is_packed:
-        if block_size == -1:
-          _capi.check(L.qmm_w4a16_perchannel_packed(*args, variant, st))
-        else:
-          _capi.check(L.qmm_w4a16_blockwise_packed(*args, block_size, variant, st))
+      return _qm._w8a8(x2, w, s32, zp32, out_dtype)
+    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    st = _capi.stream_ptr(x.device)
+    args = (x2.data_ptr(), _capi.dtype_code(x2.dtype), w.data_ptr(), s32.data_ptr(), _capi.ptr(zp32),
+            out.data_ptr(), _capi.dtype_code(out_dtype), M, N, K)
+    if weight_is_packed:
+      if block_size == -1:
+        _capi.check(L.qmm_w4a16_perchannel_packed(*args, variant, st))
       else:
-        if block_size == -1:
-          _capi.check(L.qmm_w8a16_perchannel(*args, variant, st))
-        else:
-          raise NotImplementedError(
-              "blockwise int8 weights in [N,K] layout are not supported; use the reference layout "
-              "[K/bs, bs, N] with torch.ops.xla.quantized_matmul, or pack int4 weights")
-  return out.reshape(x.shape[:-1] + (N,))
+        _capi.check(L.qmm_w4a16_blockwise_packed(*args, block_size, variant, st))
+    else:
+      if block_size == -1:
+        _capi.check(L.qmm_w8a16_perchannel(*args, variant, st))
+      else:
+        raise NotImplementedError(
+            "blockwise int8 weights in [N,K] layout are not supported; use the reference layout "
+            "[K/bs, bs, N] with torch.ops.xla.quantized_matmul, or pack int4 weights")
+    return out
+
+  out = _capi.on_device(x.device, run)
+  return out if x.dim() == 2 else out.reshape(x.shape[:-1] + (N,))
 
 
 def _meta(x, w, scaler, zero_point=None, block_size=-1, int4_weight=False, weight_is_packed=False,

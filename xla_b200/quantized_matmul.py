@@ -133,6 +133,8 @@ def _rows(x):
   """x as a contiguous [M, K] matrix."""
   if x.dtype not in (torch.float32, torch.bfloat16, torch.float16):
     raise TypeError(f"quantized_matmul: activation dtype {x.dtype} is not supported")
+  if x.dim() == 2 and x.is_contiguous():
+    return x  # the common case: no view to build
   k = x.shape[-1]
   x2 = x.reshape(-1, k)
   return x2 if x2.is_contiguous() else x2.contiguous()
@@ -190,19 +192,21 @@ def quantized_matmul_cuda(x, w, scaler, zero_point=None, block_size=-1, int4_wei
   w = w if w.is_contiguous() else w.contiguous()
   scaler32, zp32 = _f32(scaler), _f32(zero_point)
   L = _capi.lib()
-  with torch.cuda.device(x.device):
+
+  def run():
     if quantize_activation:
-      out = _w8a8(x2, w, scaler32, zp32, out_dtype)
+      return _w8a8(x2, w, scaler32, zp32, out_dtype)
+    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    args = (x2.data_ptr(), _capi.dtype_code(x2.dtype), w.data_ptr(), scaler32.data_ptr(), _capi.ptr(zp32),
+            out.data_ptr(), _capi.dtype_code(out_dtype), M, N, K)
+    if block_size == -1:
+      _capi.check(L.qmm_w8a16_perchannel(*args, _capi.VARIANTS[_variant], _capi.stream_ptr(x.device)))
     else:
-      out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-      args = (_capi.ptr(x2), _capi.dtype_code(x2.dtype), _capi.ptr(w), _capi.ptr(scaler32), _capi.ptr(zp32),
-              _capi.ptr(out), _capi.dtype_code(out_dtype), M, N, K)
-      if block_size == -1:
-        _capi.check(L.qmm_w8a16_perchannel(*args, _capi.VARIANTS[_variant], _capi.stream_ptr(x.device)))
-      else:
-        _capi.check(L.qmm_blockwise_sbn(*args, block_size, _capi.VARIANTS[_variant],
-                                        _capi.stream_ptr(x.device)))
-  return out.reshape(x.shape[:-1] + (N,))
+      _capi.check(L.qmm_blockwise_sbn(*args, block_size, _capi.VARIANTS[_variant], _capi.stream_ptr(x.device)))
+    return out
+
+  out = _capi.on_device(x.device, run)
+  return out if x.dim() == 2 else out.reshape(x.shape[:-1] + (N,))
 
 
 def quantized_matmul_meta(x, w, scaler, zero_point=None, block_size=-1, int4_weight=False,
