@@ -191,27 +191,56 @@ __global__ void __launch_bounds__(kThreads)
 
   int isum = 0;
   uint2* qv = reinterpret_cast<uint2*>(xq + m * K);
+  if (regular) {
+    // Everything after the quotient stays on the FMA and integer pipes (no conversion-unit instruction):
+    //   bf16 rounding   Veltkamp split with 2^16 + 1: g = q * 65537, qb = g + (q - g) is q rounded to 8
+    //                   significant bits, ties to even (each step is one correctly rounded operation; the
+    //                   explicit _rn intrinsics keep the compiler from fusing them)
+    //   rint -> int     qb + 1.5 * 2^23 leaves the integer, rounded ties-to-even, in the low mantissa bits
+    //   int8            clamp (or wrap) in integers, bytes gathered with prmt, row sum with dp4a
 #pragma unroll
-  for (int c = 0; c < CHUNKS; ++c) {
-    const int i = tid + c * kThreads;
-    const uint32_t w[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
-    uint32_t packed[2] = {0, 0};
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int i = tid + c * kThreads;
+      const uint32_t w[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
+      int qi[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float xv = __uint_as_float((j & 1) ? (w[j >> 1] & 0xffff0000u) : (w[j >> 1] << 16));
-      float q;
-      if (regular) {
+      for (int j = 0; j < 8; ++j) {
+        const float xv = __uint_as_float((j & 1) ? (w[j >> 1] & 0xffff0000u) : (w[j >> 1] << 16));
         const float q0 = xv * rcp;
         const float r = fmaf(-q0, scale, xv);
-        q = fmaf(r, rcp, q0);
-      } else {
-        q = __fdiv_rn(xv, scale);
+        const float q = fmaf(r, rcp, q0);
+        const float g = __fmul_rn(q, 65537.f);
+        const float qb = __fadd_rn(g, __fsub_rn(q, g));
+        int t = __float_as_int(__fadd_rn(qb, 12582912.f)) - 0x4B400000;
+        if (saturate) t = max(-128, min(127, t));
+        qi[j] = t;
       }
-      const int8_t qi = to_int8(rintf(round_to<__nv_bfloat16>(q)), saturate != 0);
-      isum += qi;
-      packed[j >> 2] |= ((uint32_t)(uint8_t)qi) << (8 * (j & 3));
+      uint32_t packed[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t lo = __byte_perm((uint32_t)qi[4 * h], (uint32_t)qi[4 * h + 1], 0x0040);
+        const uint32_t hi = __byte_perm((uint32_t)qi[4 * h + 2], (uint32_t)qi[4 * h + 3], 0x0040);
+        packed[h] = __byte_perm(lo, hi, 0x5410);
+        isum = __dp4a((int)packed[h], 0x01010101, isum);
+      }
+      if (i < nvec) qv[i] = make_uint2(packed[0], packed[1]);
     }
-    if (i < nvec) qv[i] = make_uint2(packed[0], packed[1]);
+  } else {
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int i = tid + c * kThreads;
+      const uint32_t w[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
+      uint32_t packed[2] = {0, 0};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xv = __uint_as_float((j & 1) ? (w[j >> 1] & 0xffff0000u) : (w[j >> 1] << 16));
+        const float q = __fdiv_rn(xv, scale);
+        const int8_t qi = to_int8(rintf(round_to<__nv_bfloat16>(q)), saturate != 0);
+        isum += qi;
+        packed[j >> 2] |= ((uint32_t)(uint8_t)qi) << (8 * (j & 3));
+      }
+      if (i < nvec) qv[i] = make_uint2(packed[0], packed[1]);
+    }
   }
   if (rowsum) {
 #pragma unroll
