@@ -293,6 +293,7 @@ def tp_mlp_times(dev, stream, g, world, rank, peaks, Ms=(1, 64, 512)):
   gate_s, up_s, down_s = mks(H, fl_), mks(H, fl_), mks(fl_, hl)
   op = torch.ops.xla_b200.quantized_matmul_packed
   res = {}
+  gu = None
   for M in Ms:
     x = torch.randn(M, H, generator=g, device=dev).bfloat16()
 
@@ -329,6 +330,29 @@ def tp_mlp_times(dev, stream, g, world, rank, peaks, Ms=(1, 64, 512)):
     res[f"M{M}"] = {"us_per_mlp": us, "tokens_per_s": M / (us * 1e-6), "gb_per_s_per_gpu": byt / us / 1e3,
                     "frac_of_hbm_peak": byt / us / 1e3 / peaks["hbm_gbs"],
                     "tflops_per_gpu": 3 * 2.0 * M * fl_ * H / us / 1e6, "timing": how}
+    if M <= 32 and fl_ % 8 == 0:
+      # the same MLP with gate, up and silu(gate) * up in one kernel (one weight stream of 2 * F/G rows)
+      if gu is None:
+        import xla_b200
+        gu = xla_b200.interleave_gate_up(gate_w, up_w, gate_s, up_s, BS)
+
+      def mlp_fused(i):
+        h = torch.ops.xla_b200.quantized_gate_up(x, gu[0], gu[1], block_size=BS, int4_weight=True, weight_is_packed=True,
+                                                 out_dtype=torch.bfloat16)
+        y = op(h, down_w, down_s, block_size=BS, int4_weight=True, weight_is_packed=True, out_dtype=torch.bfloat16)
+        if world > 1:
+          dist.all_reduce(y)
+        return y
+
+      try:
+        usf = time_graph(mlp_fused, stream, reps=4, iters=3)
+        if world > 1:
+          t = torch.tensor([usf], dtype=torch.float64, device=dev)
+          dist.all_reduce(t, op=dist.ReduceOp.MAX)
+          usf = float(t.item())
+        res[f"M{M}"]["us_per_mlp_fused_gate_up"] = usf
+      except Exception as e:
+        res[f"M{M}"]["us_per_mlp_fused_gate_up"] = f"not measured ({type(e).__name__})"
   return res
 
 

@@ -120,6 +120,21 @@ QMM_API int qmm_w4a16_perchannel_packed(const void* x, int x_dtype, const uint8_
                                 int64_t K, int variant, void* stream);
 
 /*
+ * Fused gate + up projection of a gated MLP for decode batches (1 <= M <= 32, bf16/f16 activations):
+ *   out[m, j] = silu(g[m, j]) * u[m, j],   g = x . dequant(Wgate)^T,  u = x . dequant(Wup)^T,  out: [M, N2/2]
+ * `w` holds both projections as N2 = 2 * out_features K-minor rows (int8 [N2,K] for wbits == 8, packed int4
+ * uint8 [N2,K/2] for wbits == 4) in groups of 16: rows 16i..16i+7 are gate rows 8i..8i+7, rows 16i+8..16i+15
+ * the up rows of the same outputs; `scale` (f32 [N2], or [K/block_size, N2] when block_size > 0, else pass 0)
+ * follows the same row order.  Both dot products and the activation are computed in fp32 and rounded once.
+ * Replaces: nothing in the reference - it issues two quantized_matmul calls and leaves silu(gate) * up to XLA's
+ * fusion; the formula per projection is the one of xla_quantized_matmul.py:152-170.
+ * Returns QMM_ERR_UNSUPPORTED outside the decode kernels' range (callers then run the two projections as one
+ * [N2]-row linear and apply the activation themselves).
+ */
+QMM_API int qmm_gate_up_decode(int wbits, const void* x, int x_dtype, const void* w, const float* scale, void* out,
+                       int out_dtype, int64_t M, int64_t N2, int64_t K, int64_t block_size, void* stream);
+
+/*
  * Per-token dynamic activation quantizer:
  *   amax = max_k |x[m,k]|; s = amax / 127 (rounded to x's dtype); xq = rint(x / s) (quotient
  *   rounded to x's dtype first) -> int8.

@@ -556,6 +556,61 @@ def test_tmem_rounds_and_passes(N):
 
 
 # ---------------------------------------------------------------------------------------------
+# fused gate + up projection with silu(gate) * up, and concatenated projections
+# ---------------------------------------------------------------------------------------------
+
+
+def _silu_mul(g, u):
+  g, u = g.double(), u.double()
+  return g / (1 + torch.exp(-g)) * u
+
+
+@pytest.mark.parametrize("M", [1, 8, 20, 32, 40])
+@pytest.mark.parametrize("mode", ["w4_blockwise", "w8_per_channel"])
+def test_gate_up_fused(M, mode):
+  """One kernel for both projections and the activation (M <= 32); the stacked-linear path above that."""
+  g = qc.gen(40)
+  N, K, bs = 1000 - 1000 % 8, 1024, 128
+  x = qc.activations(g, M, K)
+  if mode == "w4_blockwise":
+    wg, wu = qc.int4_weight(g, N, K), qc.int4_weight(g, N, K)
+    sg, su = qc.blockwise_scale(g, K // bs, N), qc.blockwise_scale(g, K // bs, N)
+    gate = qo.quantized_matmul(x.float(), qc.to_sbn(wg, bs), sg, block_size=bs, dot_round=None)
+    up = qo.quantized_matmul(x.float(), qc.to_sbn(wu, bs), su, block_size=bs, dot_round=None)
+    w, s = xla_b200.interleave_gate_up(xla_b200.pack_int4(cu(wg)), xla_b200.pack_int4(cu(wu)), cu(sg), cu(su), bs)
+    out = torch.ops.xla_b200.quantized_gate_up(cu(x), w, s, block_size=bs, int4_weight=True, weight_is_packed=True)
+  else:
+    wg, wu = qc.int8_weight(g, N, K), qc.int8_weight(g, N, K)
+    sg, su = qc.per_channel_scale(g, N), qc.per_channel_scale(g, N)
+    gate = qo.quantized_matmul(x, wg, sg, dot_round=None)
+    up = qo.quantized_matmul(x, wu, su, dot_round=None)
+    w, s = xla_b200.interleave_gate_up(cu(wg), cu(wu), cu(sg), cu(su))
+    out = torch.ops.xla_b200.quantized_gate_up(cu(x), w, s)
+  assert out.shape == (M, N) and out.dtype == torch.float32
+  assert qo.max_abs_rel(out, _silu_mul(gate, up)) < TOL_F32
+  # bf16 output: one rounding of the fp32 result
+  if mode == "w4_blockwise":
+    out16 = torch.ops.xla_b200.quantized_gate_up(cu(x), w, s, block_size=bs, int4_weight=True, weight_is_packed=True,
+                                                 out_dtype=torch.bfloat16)
+    assert out16.dtype == torch.bfloat16
+    assert qo.max_abs_rel(out16, _silu_mul(gate, up)) < TOL_BF16
+
+
+def test_concat_projections_qkv():
+  """q, k, v read the same activations: one weight stream, outputs split afterwards."""
+  g = qc.gen(41)
+  K, sizes = 1024, [512, 128, 128]
+  x = qc.activations(g, 4, K)
+  ws = [qc.int8_weight(g, n, K) for n in sizes]
+  ss = [qc.per_channel_scale(g, n) for n in sizes]
+  w, s, got_sizes = xla_b200.concat_projections([cu(t) for t in ws], [cu(t) for t in ss])
+  assert got_sizes == sizes
+  y = packed_op(cu(x), w, s)
+  for part, wi, si in zip(xla_b200.split_outputs(y, sizes), ws, ss):
+    assert qo.max_abs_rel(part, qo.quantized_matmul(x, wi, si, dot_round=None)) < TOL_F32
+
+
+# ---------------------------------------------------------------------------------------------
 # the reference's module-level tests, replayed on the GPU (test/quantized_ops/test_quantized_matmul.py)
 # ---------------------------------------------------------------------------------------------
 

@@ -137,3 +137,26 @@ def test_rtn_quantizer_layouts_and_reconstruction():
   net = wp.swap_linears(Net(), n_bits=8)
   assert isinstance(net.a, xla_b200.XlaQuantizedLinear) and isinstance(net.b[1], xla_b200.XlaQuantizedLinear)
   assert isinstance(net.b[0], torch.nn.Linear)  # has a bias: left alone
+
+
+def test_gate_up_interleave_round_trip():
+  """Row order of the stacked gate/up weight: eight gate rows, eight up rows, and back."""
+  from xla_b200 import mlp
+  n, k = 24, 6
+  wg = torch.arange(n * k, dtype=torch.int32).reshape(n, k)
+  wu = -wg - 1
+  w, s = mlp.interleave_gate_up(wg, wu, torch.arange(n, dtype=torch.float32), -torch.arange(n, dtype=torch.float32) - 1)
+  assert w.shape == (2 * n, k) and s.shape == (2 * n,)
+  assert torch.equal(w[0:8], wg[0:8]) and torch.equal(w[8:16], wu[0:8]) and torch.equal(w[16:24], wg[8:16])
+  # a [M, 2N] result in that column order splits back into gate and up
+  y = torch.stack([s, 2 * s])
+  g, u = mlp._deinterleave(y)
+  assert torch.equal(g[0], torch.arange(n, dtype=torch.float32)) and torch.equal(u[0], -torch.arange(n, dtype=torch.float32) - 1)
+  # blockwise scales [S, N] interleave along N
+  sg, su = torch.zeros(3, n), torch.ones(3, n)
+  _, s2 = mlp.interleave_gate_up(wg, wu, sg, su, block_size=2)
+  assert s2.shape == (3, 2 * n) and torch.equal(s2[:, 0:8], sg[:, 0:8]) and torch.equal(s2[:, 8:16], su[:, 0:8])
+  w3, s3, sizes = mlp.concat_projections([wg, wu[:8]], [sg[0], su[0, :8]])
+  assert sizes == [n, 8] and w3.shape == (n + 8, k) and s3.shape == (n + 8,)
+  parts = mlp.split_outputs(torch.zeros(2, n + 8), sizes)
+  assert [p.shape[-1] for p in parts] == sizes

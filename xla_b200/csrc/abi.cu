@@ -279,6 +279,25 @@ int qmm_w4a16_blockwise_packed(const void* x, int x_dtype, const uint8_t* wp, co
   }
 }
 
+int qmm_gate_up_decode(int wbits, const void* x, int x_dtype, const void* w, const float* scale, void* out,
+                       int out_dtype, int64_t M, int64_t N2, int64_t K, int64_t block_size, void* stream) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (wbits != 4 && wbits != 8) return fail(QMM_ERR_BAD_SHAPE, "gate_up_decode: wbits must be 4 or 8, got %d", wbits);
+  if (!x || !w || !scale || !out) return fail(QMM_ERR_NULL, "gate_up_decode: null pointer");
+  if (M < 0 || N2 < 0 || K < 0) return fail(QMM_ERR_BAD_SHAPE, "gate_up_decode: negative size");
+  if (N2 % 16 != 0) return fail(QMM_ERR_BAD_SHAPE, "gate_up_decode: N2 must be a multiple of 16, got %lld", (long long)N2);
+  if (block_size < 0 || (block_size > 0 && K % block_size != 0))
+    return fail(QMM_ERR_BAD_SHAPE, "gate_up_decode: K (%lld) must be a multiple of block_size (%lld)", (long long)K,
+                (long long)block_size);
+  if (M == 0 || N2 == 0) return QMM_OK;
+  if (!decode_mma_supported(wbits, M, N2, K, block_size, x, x_dtype, w, false))
+    return fail(QMM_ERR_UNSUPPORTED, "gate_up_decode: needs 1<=M<=32, bf16/f16 activations, K a multiple of %d, 16-byte "
+                "aligned x/w (M=%lld N2=%lld K=%lld bs=%lld)", 512 / wbits, (long long)M, (long long)N2, (long long)K,
+                (long long)block_size);
+  log_choice("gate_up_decode", "mma", M, N2, K);
+  return launch_decode_mma(wbits, x, x_dtype, w, scale, out, out_dtype, M, N2, K, block_size, st, 1);
+}
+
 int qmm_w4a16_perchannel_packed(const void* x, int x_dtype, const uint8_t* wp, const float* scale,
                                 const float* zp, void* out, int out_dtype, int64_t M, int64_t N,
                                 int64_t K, int variant, void* stream) {

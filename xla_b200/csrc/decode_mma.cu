@@ -105,6 +105,12 @@ __device__ __forceinline__ uint32_t sub_bias(uint32_t p, float bias) {
   }
 }
 
+// Fused MLP epilogue: the weight rows are stored in groups of 16, eight rows of the gate projection followed
+// by the eight rows of the up projection for the same outputs; the kernel then writes silu(gate) * up, one
+// column per pair, computed in fp32 from the fp32 accumulators.
+__device__ __forceinline__ float silu_mul(float gate, float up) { return gate / (1.f + expf(-gate)) * up; }
+__device__ __forceinline__ int64_t gate_up_column(int64_t n) { return ((n >> 4) << 3) + (n & 7); }
+
 // NT = number of 8-token tiles (M <= 8*NT); RG = 16-row groups per CTA (each warp converts RG groups per
 // step and reuses its activation registers for all of them); WARPS = warps splitting K.
 // One "fold" = the end of a scale block (blockwise) or of a single step (per-channel): the partial tile,
@@ -113,7 +119,7 @@ template <int WBITS, typename XT, int NT, int RG, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
     decode_mma_kernel(const XT* __restrict__ x, const uint8_t* __restrict__ w, const float* __restrict__ scale,
                       void* __restrict__ out, int out_dt, int M, int64_t N, int64_t K, int steps_per_block,
-                      int spb_shift, int blockwise) {
+                      int spb_shift, int blockwise, int gate_up) {
   constexpr int VPS = 512 / WBITS;      // values of one weight row per step: 128 (int4) or 64 (int8)
   constexpr int VPL = VPS / 4;          // values per lane per row per step: 32 or 16
   constexpr int XREGS = VPL / 2;        // packed activation pairs per lane per token tile: 16 or 8
@@ -325,7 +331,16 @@ __global__ void __launch_bounds__(WARPS * 32)
 #pragma unroll
       for (int wi = 0; wi < WARPS; ++wi) v += s_part[wi][row][tok];
       if (!blockwise) v *= __ldg(scale + n);
-      store_from_f32(out, (int64_t)tok * N + n, out_dt, v);
+      if (!gate_up) {
+        store_from_f32(out, (int64_t)tok * N + n, out_dt, v);
+      } else if ((row & 8) == 0) {
+        // rows come in groups of 16: eight gate rows, then the eight up rows of the same outputs
+        float u = 0.f;
+#pragma unroll
+        for (int wi = 0; wi < WARPS; ++wi) u += s_part[wi][row + 8][tok];
+        if (!blockwise) u *= __ldg(scale + n + 8);
+        store_from_f32(out, (int64_t)tok * (N >> 1) + gate_up_column(n), out_dt, silu_mul(v, u));
+      }
     }
   }
 }
@@ -375,7 +390,7 @@ template <int WBITS, typename XT, int NT>
 __global__ void __launch_bounds__(kStagedWarps * 32, 1)
     decode_mma_staged_kernel(const XT* __restrict__ x, const uint8_t* __restrict__ w, const float* __restrict__ scale,
                              void* __restrict__ out, int out_dt, int M, int N, int K, int steps_per_block,
-                             int spb_shift, int blockwise, int tiles, int TR, int WK, int rounds) {
+                             int spb_shift, int blockwise, int tiles, int TR, int WK, int rounds, int gate_up) {
   constexpr int VPS = 512 / WBITS;            // weight values per row per step
   constexpr int UPS = VPS * 2 / 16;           // 16-byte activation units per token per step: 16 or 8
   constexpr int UPL = UPS / 4;                // units per lane per step: 4 or 2
@@ -602,7 +617,14 @@ __global__ void __launch_bounds__(kStagedWarps * 32, 1)
         float v = 0.f;
         for (int j = 0; j < WK; ++j) v += red[((slot * WK + j) * ROWS_X + tok) * kRedPitch + row];
         if (!blockwise) v *= __ldg(scale + n);
-        store_from_f32(out, (int64_t)tok * N + n, out_dt, v);
+        if (!gate_up) {
+          store_from_f32(out, (int64_t)tok * N + n, out_dt, v);
+        } else if ((row & 8) == 0) {
+          float u = 0.f;
+          for (int j = 0; j < WK; ++j) u += red[((slot * WK + j) * ROWS_X + tok) * kRedPitch + row + 8];
+          if (!blockwise) u *= __ldg(scale + n + 8);
+          store_from_f32(out, (int64_t)tok * (N >> 1) + gate_up_column(n), out_dt, silu_mul(v, u));
+        }
       }
     }
     __syncthreads();  // the ring is refilled next round
@@ -628,7 +650,7 @@ cudaError_t launch_pdl(Kernel kern, unsigned grid, unsigned block, size_t smem_b
 
 template <int WBITS, typename XT, int NT>
 cudaError_t launch_staged(const XT* xp, const uint8_t* wp, const float* scale, void* out, int out_dt, int64_t M,
-                          int64_t N, int64_t K, int spb, int shift, int bw, cudaStream_t st) {
+                          int64_t N, int64_t K, int spb, int shift, int bw, int gate_up, cudaStream_t st) {
   constexpr int VPS = 512 / WBITS;
   constexpr int PITCH = kChunkSteps * (VPS * 2 / 16) * 16 + 16;
   constexpr size_t kSmem = 2 * (size_t)(NT * 8) * PITCH;
@@ -652,12 +674,12 @@ cudaError_t launch_staged(const XT* xp, const uint8_t* wp, const float* scale, v
   const int wk = std::min(kStagedWarps / tr, 8);   // warps sharing the K steps of one tile
   const int rounds = (int)ceil_div(per_cta, tr);
   return launch_pdl(kern, (unsigned)grid, kStagedWarps * 32, kSmem, st, xp, wp, scale, out, out_dt, (int)M, (int)N, (int)K, spb,
-                    shift, bw, tiles, tr, wk, rounds);
+                    shift, bw, tiles, tr, wk, rounds, gate_up);
 }
 
 template <int WBITS, typename XT>
 int launch_nt(const void* x, const void* w, const float* scale, void* out, int out_dt, int64_t M, int64_t N,
-              int64_t K, int64_t block_size, cudaStream_t st) {
+              int64_t K, int64_t block_size, int gate_up, cudaStream_t st) {
   constexpr int VPS = 512 / WBITS;
   const int spb = block_size > 0 ? (int)(block_size / VPS) : 1;
   int shift = -1;
@@ -670,16 +692,16 @@ int launch_nt(const void* x, const void* w, const float* scale, void* out, int o
   const uint8_t* wp = reinterpret_cast<const uint8_t*>(w);
 #define QMM_DECODE_LAUNCH(NT, RG, WARPS)                                                                        \
   launch_pdl(decode_mma_kernel<WBITS, XT, NT, RG, WARPS>, (unsigned)ceil_div(N, 16 * RG), WARPS * 32, 0, st, xp, wp, \
-             scale, out, out_dt, (int)M, N, K, spb, shift, bw)
+             scale, out, out_dt, (int)M, N, K, spb, shift, bw, gate_up)
   // one token tile: many small CTAs, activations through L1 (64 KB for 8 tokens of 4096);
   // two or four tiles: one CTA per SM with the activations staged in shared memory
   cudaError_t err;
   if (M <= 8)
     err = QMM_DECODE_LAUNCH(1, 1, 4);
   else if (M <= 16)
-    err = launch_staged<WBITS, XT, 2>(xp, wp, scale, out, out_dt, M, N, K, spb, shift, bw, st);
+    err = launch_staged<WBITS, XT, 2>(xp, wp, scale, out, out_dt, M, N, K, spb, shift, bw, gate_up, st);
   else
-    err = launch_staged<WBITS, XT, 4>(xp, wp, scale, out, out_dt, M, N, K, spb, shift, bw, st);
+    err = launch_staged<WBITS, XT, 4>(xp, wp, scale, out, out_dt, M, N, K, spb, shift, bw, gate_up, st);
   if (err != cudaSuccess) {
     cudaGetLastError();
     return fail(QMM_ERR_LAUNCH, "decode_mma_kernel launch: %s", cudaGetErrorString(err));
@@ -704,18 +726,21 @@ bool decode_mma_supported(int wbits, int64_t M, int64_t N, int64_t K, int64_t bl
 }
 
 int launch_decode_mma(int wbits, const void* x, int x_dt, const void* w, const float* scale, void* out, int out_dt,
-                      int64_t M, int64_t N, int64_t K, int64_t block_size, cudaStream_t st) {
+                      int64_t M, int64_t N, int64_t K, int64_t block_size, cudaStream_t st, int gate_up) {
+  if (gate_up && N % 16 != 0)
+    return fail(QMM_ERR_BAD_SHAPE, "fused gate/up epilogue: the interleaved weight needs a multiple of 16 rows, got %lld",
+                (long long)N);
   if (!decode_mma_supported(wbits, M, N, K, block_size, x, x_dt, w, false))
     return fail(QMM_ERR_UNSUPPORTED,
                 "decode kernel: needs bf16/f16 activations, 1<=M<=32, K a multiple of %d, block_size a multiple of %d, "
                 "16-byte aligned x/w, no zero point (M=%lld N=%lld K=%lld bs=%lld)",
                 512 / wbits, 512 / wbits, (long long)M, (long long)N, (long long)K, (long long)block_size);
   if (wbits == 4) {
-    if (x_dt == QMM_BF16) return launch_nt<4, __nv_bfloat16>(x, w, scale, out, out_dt, M, N, K, block_size, st);
-    return launch_nt<4, __half>(x, w, scale, out, out_dt, M, N, K, block_size, st);
+    if (x_dt == QMM_BF16) return launch_nt<4, __nv_bfloat16>(x, w, scale, out, out_dt, M, N, K, block_size, gate_up, st);
+    return launch_nt<4, __half>(x, w, scale, out, out_dt, M, N, K, block_size, gate_up, st);
   }
-  if (x_dt == QMM_BF16) return launch_nt<8, __nv_bfloat16>(x, w, scale, out, out_dt, M, N, K, block_size, st);
-  return launch_nt<8, __half>(x, w, scale, out, out_dt, M, N, K, block_size, st);
+  if (x_dt == QMM_BF16) return launch_nt<8, __nv_bfloat16>(x, w, scale, out, out_dt, M, N, K, block_size, gate_up, st);
+  return launch_nt<8, __half>(x, w, scale, out, out_dt, M, N, K, block_size, gate_up, st);
 }
 
 }  // namespace qmm

@@ -47,8 +47,10 @@ int launch_gemv_sbn(const void* x, int x_dt, const int8_t* w, const float* scale
 // activations, no zero point).  block_size == 0 means per-channel scales.
 bool decode_mma_supported(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size, const void* x, int x_dt,
                           const void* w, bool has_zp);
+// gate_up != 0: the weight rows are interleaved gate/up groups of eight and the kernel writes
+// silu(gate) * up as [M, N/2].
 int launch_decode_mma(int wbits, const void* x, int x_dt, const void* w, const float* scale, void* out, int out_dt,
-                      int64_t M, int64_t N, int64_t K, int64_t block_size, cudaStream_t st);
+                      int64_t M, int64_t N, int64_t K, int64_t block_size, cudaStream_t st, int gate_up = 0);
 
 // ---- decode_tc.cu -------------------------------------------------------------------------
 // Decode kernel on tcgen05 with the weight operand written to tensor memory (M <= 32, bf16/f16
