@@ -124,12 +124,16 @@ class C2Decode:
     return self.op(self.x[m] if x is None else x, self.wp[i], self.scale[i], block_size=self.BS, int4_weight=True,
                    weight_is_packed=True, out_dtype=torch.bfloat16)
 
+  forced = "auto"  # kernel family forced with --variant
+
   def tokens_per_step(self, reps):
     return reps * sum(self.MS)
 
 
 def variant_name(m, N, K, bs):
   from xla_b200 import _capi
+  if C2Decode.forced != "auto":
+    return C2Decode.forced
   return _capi.lib().qmm_variant_for(_capi.OP_W4A16_BLOCKWISE_PACKED, m, N, K, bs, 0).decode()
 
 
@@ -393,6 +397,10 @@ def run_ours(args, rank, world, local_rank):
     dist.init_process_group("nccl", device_id=dev)
   peaks = measured_peaks()
   wl = C2Decode(dev, args.seed + rank)
+  if args.variant != "auto":
+    import xla_b200.quantized_matmul as _qm_mod
+    C2Decode.forced = args.variant
+    _qm_mod._variant = args.variant  # what xla_b200.force_variant sets, for the whole run
   reps = args.reps
   stream = torch.cuda.Stream(device=dev)
 
@@ -588,6 +596,9 @@ def main():
   ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
   ap.add_argument("--no-cpu-baseline", action="store_true")
   ap.add_argument("--headline-only", action="store_true", help="skip the other configurations / the TP MLP")
+  ap.add_argument("--variant", default="auto", choices=["auto", "generic", "gemv", "tcgen05", "mma", "tmem"],
+                  help="force one kernel family for the headline workload (profiling a non-default kernel); "
+                       "the default lets the library choose by shape")
   args = ap.parse_args()
   args.warmup = max(args.warmup, 3)
   rank = int(os.environ.get("RANK", "0"))
