@@ -120,6 +120,17 @@ QMM_API int qmm_w4a16_perchannel_packed(const void* x, int x_dtype, const uint8_
                                 int64_t K, int variant, void* stream);
 
 /*
+ * Blockwise weight-only linear on int8 weights stored K-minor (w: int8 [N,K]; scale, zp: f32 [K/block_size, N]):
+ *   out[m,n] = sum_b scale[b,n] * (sum_{k in block b} x[m,k] * w[n,k])  -  sum_b zp[b,n] * sum_{k in block b} x[m,k]
+ * The arithmetic of qmm_blockwise_sbn on the layout the decode and tensor-core kernels stream; callers transpose
+ * a reference-layout weight [K/bs, bs, N] once (the module does).
+ * Replaces: the blockwise einsum pair of the reference (xla_quantized_matmul.py:120-124, :165-170).
+ */
+QMM_API int qmm_w8a16_blockwise(const void* x, int x_dtype, const int8_t* w, const float* scale, const float* zp,
+                        void* out, int out_dtype, int64_t M, int64_t N, int64_t K, int64_t block_size, int variant,
+                        void* stream);
+
+/*
  * Fused gate + up projection of a gated MLP for decode batches (1 <= M <= 32, bf16/f16 activations):
  *   out[m, j] = silu(g[m, j]) * u[m, j],   g = x . dequant(Wgate)^T,  u = x . dequant(Wup)^T,  out: [M, N2/2]
  * `w` holds both projections as N2 = 2 * out_features K-minor rows (int8 [N2,K] for wbits == 8, packed int4

@@ -556,6 +556,45 @@ def test_tmem_rounds_and_passes(N):
 
 
 # ---------------------------------------------------------------------------------------------
+# int8 blockwise weights stored K-minor (what the module keeps for the fast kernels)
+# ---------------------------------------------------------------------------------------------
+
+
+@pytest.mark.parametrize("M", [1, 8, 20, 64, 300])
+@pytest.mark.parametrize("with_zp", [False, True])
+def test_w8a16_blockwise_k_minor(M, with_zp):
+  g = qc.gen(50)
+  N, K, bs = 1000, 1024, 128
+  x = qc.activations(g, M, K)
+  w_nk = qc.int8_weight(g, N, K)
+  s = qc.blockwise_scale(g, K // bs, N)
+  zp = (qc.blockwise_scale(g, K // bs, N) - 0.02) if with_zp else None
+  exact = qo.quantized_matmul(x.float(), qc.to_sbn(w_nk, bs), s, zp, block_size=bs, dot_round=None)
+  out = packed_op(cu(x), cu(w_nk), cu(s), None if zp is None else cu(zp), block_size=bs)
+  assert out.dtype == torch.float32 and out.shape == (M, N)
+  assert qo.max_abs_rel(out, exact) < TOL_F32
+
+
+def test_module_int8_blockwise_uses_k_minor_copy():
+  """XlaQuantizedLinear(block_size>0, int8): reference layout in, K-minor copy built once, same results as the op."""
+  g = qc.gen(51)
+  N, K, bs, M = 512, 1024, 128, 4
+  x = qc.activations(g, M, K)
+  w_nk = qc.int8_weight(g, N, K)
+  s = qc.blockwise_scale(g, K // bs, N)
+  m = xla_b200.XlaQuantizedLinear(K, N, is_symmetric=True, block_size=bs)
+  m.load_quantized_weight(cu(qc.to_sbn(w_nk, bs)), cu(s))
+  y = m(cu(x))
+  w_copy, is_packed = m._packed_weight()
+  assert not is_packed and w_copy.shape == (N, K) and torch.equal(w_copy.cpu(), w_nk)
+  exact = qo.quantized_matmul(x.float(), qc.to_sbn(w_nk, bs), s, block_size=bs, dot_round=None)
+  assert qo.max_abs_rel(y, exact) < TOL_F32
+  # the reference-layout operator gives the same numbers through the any-shape kernels
+  y_ref = torch.ops.xla.quantized_matmul(cu(x), cu(qc.to_sbn(w_nk, bs)), cu(s), None, block_size=bs)
+  assert qo.max_abs_rel(y_ref, exact) < TOL_F32
+
+
+# ---------------------------------------------------------------------------------------------
 # fused gate + up projection with silu(gate) * up, and concatenated projections
 # ---------------------------------------------------------------------------------------------
 

@@ -28,6 +28,7 @@ SIGNATURES = {
     "qmm_last_error_string": (ctypes.c_char_p, []),
     "qmm_w8a16_perchannel": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i, _p]),
     "qmm_w4a16_perchannel_packed": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i, _p]),
+    "qmm_w8a16_blockwise": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _p]),
     "qmm_gate_up_decode": (_i, [_i, _p, _i, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _p]),
     "qmm_blockwise_sbn": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _p]),
     "qmm_w4a16_blockwise_packed": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _p]),

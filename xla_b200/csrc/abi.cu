@@ -279,6 +279,40 @@ int qmm_w4a16_blockwise_packed(const void* x, int x_dtype, const uint8_t* wp, co
   }
 }
 
+int qmm_w8a16_blockwise(const void* x, int x_dtype, const int8_t* w, const float* scale, const float* zp, void* out,
+                        int out_dtype, int64_t M, int64_t N, int64_t K, int64_t block_size, int variant, void* stream) {
+  int rc = check_common(x, x_dtype, w, scale, out, out_dtype, M, N, K);
+  if (rc != QMM_OK) return rc;
+  if (block_size <= 0 || K % block_size != 0)
+    return fail(QMM_ERR_BAD_SHAPE, "input_dim should be divisible by block_size, got input_dim: %lld, block_size: %lld",
+                (long long)K, (long long)block_size);
+  if (M * N == 0) return QMM_OK;
+  cudaStream_t st = as_stream(stream);
+  if (variant == QMM_VARIANT_AUTO) variant = pick_weight_only(8, M, N, K, block_size, x, x_dtype, w, zp != nullptr);
+  switch (variant) {
+    case QMM_VARIANT_GENERIC:
+      log_choice("w8a16_blockwise", "generic", M, N, K);
+      return launch_generic_nk(false, x, x_dtype, w, scale, zp, out, out_dtype, M, N, K, block_size, st);
+    case QMM_VARIANT_GEMV:
+      log_choice("w8a16_blockwise", "gemv", M, N, K);
+      return launch_gemv_nk(8, x, x_dtype, w, scale, zp, out, out_dtype, M, N, K, block_size, st);
+    case QMM_VARIANT_MMA:
+      log_choice("w8a16_blockwise", "mma", M, N, K);
+      if (zp) return fail(QMM_ERR_UNSUPPORTED, "the register-dequant decode kernel does not take a zero point");
+      return launch_decode_mma(8, x, x_dtype, w, scale, out, out_dtype, M, N, K, block_size, st);
+    case QMM_VARIANT_TMEM:
+      log_choice("w8a16_blockwise", "tmem", M, N, K);
+      if (zp) return fail(QMM_ERR_UNSUPPORTED, "w8a16_blockwise: the tensor-memory decode kernel takes no zero point");
+      return launch_decode_tc(8, x, x_dtype, w, scale, out, out_dtype, M, N, K, block_size, st);
+    case QMM_VARIANT_TCGEN05:
+      log_choice("w8a16_blockwise", "tcgen05", M, N, K);
+      if (zp) return fail(QMM_ERR_UNSUPPORTED, "tcgen05 weight-only kernel does not take a zero point");
+      return launch_mixed_tc(8, x, x_dtype, w, scale, out, out_dtype, M, N, K, block_size, st);
+    default:
+      return fail(QMM_ERR_UNSUPPORTED, "unknown variant %d", variant);
+  }
+}
+
 int qmm_gate_up_decode(int wbits, const void* x, int x_dtype, const void* w, const float* scale, void* out,
                        int out_dtype, int64_t M, int64_t N2, int64_t K, int64_t block_size, void* stream) {
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);

@@ -125,9 +125,7 @@ def quantized_matmul_packed(x, w, scaler, zero_point=None, block_size=-1, int4_w
       if block_size == -1:
         _capi.check(L.qmm_w8a16_perchannel(*args, variant, st))
       else:
-        raise NotImplementedError(
-            "blockwise int8 weights in [N,K] layout are not supported; use the reference layout "
-            "[K/bs, bs, N] with torch.ops.xla.quantized_matmul, or pack int4 weights")
+        _capi.check(L.qmm_w8a16_blockwise(*args, block_size, variant, st))
     return out
 
   out = _capi.on_device(x.device, run)
