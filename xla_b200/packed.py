@@ -106,16 +106,18 @@ def quantized_matmul_packed(x, w, scaler, zero_point=None, block_size=-1, int4_w
   s32, zp32 = _qm._f32(scaler), _qm._f32(zero_point)
   L = _capi.lib()
   variant = _capi.VARIANTS[_qm._variant]
+  zp_after = not quantize_activation and _qm._zero_point_outside(M, x2, zero_point)
 
   def run():
     if quantize_activation:
       if weight_is_packed:
         raise NotImplementedError("W4A8 (packed int4 weights with activation quantization) is not supported")
       return _qm._w8a8(x2, w, s32, zp32, out_dtype)
-    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    kdt = torch.float32 if zp_after else out_dtype
+    out = torch.empty((M, N), dtype=kdt, device=x.device)
     st = _capi.stream_ptr(x.device)
-    args = (x2.data_ptr(), _capi.dtype_code(x2.dtype), w.data_ptr(), s32.data_ptr(), _capi.ptr(zp32),
-            out.data_ptr(), _capi.dtype_code(out_dtype), M, N, K)
+    args = (x2.data_ptr(), _capi.dtype_code(x2.dtype), w.data_ptr(), s32.data_ptr(),
+            None if zp_after else _capi.ptr(zp32), out.data_ptr(), _capi.dtype_code(kdt), M, N, K)
     if weight_is_packed:
       if block_size == -1:
         _capi.check(L.qmm_w4a16_perchannel_packed(*args, variant, st))
@@ -126,6 +128,8 @@ def quantized_matmul_packed(x, w, scaler, zero_point=None, block_size=-1, int4_w
         _capi.check(L.qmm_w8a16_perchannel(*args, variant, st))
       else:
         _capi.check(L.qmm_w8a16_blockwise(*args, block_size, variant, st))
+    if zp_after:
+      out = _qm._subtract_zero_point(out, x2, zp32, block_size).to(out_dtype)
     return out
 
   out = _capi.on_device(x.device, run)

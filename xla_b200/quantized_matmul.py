@@ -129,6 +129,22 @@ def _f32(t):
   return t.contiguous() if t.dtype == torch.float32 else t.float().contiguous()
 
 
+def _zero_point_outside(M, x2, zero_point):
+  """True when the zero-point term is applied after the kernel: the tensor-core and register-dequant
+  kernels take symmetric weights only, and the any-shape kernel that does take a zero point is far slower
+  than one of them plus a rank-S update (S = number of scale blocks)."""
+  return (zero_point is not None and M > 8 and _variant == "auto" and
+          x2.dtype in (torch.bfloat16, torch.float16))
+
+
+def _subtract_zero_point(y32, x2, zp32, block_size):
+  """y32[m,n] -= sum_b (sum_{k in block b} x[m,k]) * zp[b,n], in fp32 (the reference's second term, :159, :170)."""
+  M, K = x2.shape
+  S = 1 if block_size == -1 else K // block_size
+  xs = x2.float().reshape(M, S, K // S).sum(-1)
+  return y32.addmm_(xs, zp32.reshape(S, -1), alpha=-1.0)
+
+
 def _rows(x):
   """x as a contiguous [M, K] matrix."""
   if x.dtype not in (torch.float32, torch.bfloat16, torch.float16):
@@ -192,17 +208,22 @@ def quantized_matmul_cuda(x, w, scaler, zero_point=None, block_size=-1, int4_wei
   w = w if w.is_contiguous() else w.contiguous()
   scaler32, zp32 = _f32(scaler), _f32(zero_point)
   L = _capi.lib()
+  # per-channel weights reach the fast kernels directly; their zero point is applied afterwards
+  zp_after = block_size == -1 and not quantize_activation and _zero_point_outside(M, x2, zero_point)
 
   def run():
     if quantize_activation:
       return _w8a8(x2, w, scaler32, zp32, out_dtype)
-    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-    args = (x2.data_ptr(), _capi.dtype_code(x2.dtype), w.data_ptr(), scaler32.data_ptr(), _capi.ptr(zp32),
-            out.data_ptr(), _capi.dtype_code(out_dtype), M, N, K)
+    kdt = torch.float32 if zp_after else out_dtype
+    out = torch.empty((M, N), dtype=kdt, device=x.device)
+    args = (x2.data_ptr(), _capi.dtype_code(x2.dtype), w.data_ptr(), scaler32.data_ptr(),
+            None if zp_after else _capi.ptr(zp32), out.data_ptr(), _capi.dtype_code(kdt), M, N, K)
     if block_size == -1:
       _capi.check(L.qmm_w8a16_perchannel(*args, _capi.VARIANTS[_variant], _capi.stream_ptr(x.device)))
     else:
       _capi.check(L.qmm_blockwise_sbn(*args, block_size, _capi.VARIANTS[_variant], _capi.stream_ptr(x.device)))
+    if zp_after:
+      out = _subtract_zero_point(out, x2, zp32, -1).to(out_dtype)
     return out
 
   out = _capi.on_device(x.device, run)
