@@ -268,8 +268,10 @@ def test_blockwise_module_prepacks_int4():
 
 
 @pytest.mark.parametrize("variant", ["generic", "tcgen05"])
-@pytest.mark.parametrize("M,N,K", [(256, 512, 4096), (130, 264, 144), (16, 4096, 4096), (1, 256, 128)])
+@pytest.mark.parametrize("M,N,K", [(256, 512, 4096), (130, 264, 144), (16, 4096, 4096), (1, 256, 128),
+                                   (300, 37 * 256 + 40, 272), (512, 9472, 128)])
 def test_w8a8_vs_oracle(variant, M, N, K):
+  # the last two shapes have enough 256 x 256 tiles for the two-accumulator kernel (ragged and exact edges)
   g = qc.gen(5)
   x = qc.activations(g, M, K, outliers=True)
   w = qc.int8_weight(g, N, K)

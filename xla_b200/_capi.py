@@ -87,8 +87,13 @@ _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 def stream_ptr(device=None):
   """Handle of torch's current stream on `device` (an int usable as cudaStream_t)."""
   if _raw_stream is not None:
-    idx = torch.cuda.current_device() if device is None or device.index is None else device.index
-    return _raw_stream(idx)
+    if device is None:
+      idx = None
+    elif isinstance(device, int):
+      idx = device
+    else:
+      idx = torch.device(device).index  # accepts torch.device and strings like "cuda:0"
+    return _raw_stream(torch.cuda.current_device() if idx is None else idx)
   return torch.cuda.current_stream(device).cuda_stream
 
 

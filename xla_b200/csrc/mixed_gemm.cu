@@ -313,21 +313,22 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t b_lo0 = (uint32_t)ptx::make_sw128_kmajor_desc(ptx::smem_u32(b_base));
       int blk = 0, in_blk = 0, ti = 0;
       const uint32_t leader = lane == 0 ? 1u : 0u;
+      // ring positions advance with adds and compares only: this warp's instruction count per tile is what
+      // bounds the kernel at small token tiles, and a division by a ring depth costs as much as an MMA issue
+      int sa = 0, a_par = 0;           // operand slot of tile t and the parity of its current use
+      int sb = 0, jb = 0, b_par = 0;   // activation group slot, tile inside the group, parity
+      uint32_t a_lo = a_lo0, b_lo = b_lo0;
       for (int t = 0; t < my_tiles; ++t) {
         const int buf = blk & 1;
         if (in_blk == 0) {
           ptx::mbar_wait(&acc_empty[buf], ((blk >> 1) & 1) ^ 1, abort_flag, p.err_word, ptx::kErrWaitTmemEmpty);
           ptx::tcgen05_fence_after();  // the drain warps' tcgen05.ld of this buffer precede the overwrite
         }
-        const int sa = t % kAStages;
-        const int gb = t / kBGroup, sb = gb % kBStages, jb = t % kBGroup;
-        if (jb == 0) ptx::mbar_wait(&b_full[sb], (gb / kBStages) & 1, abort_flag, p.err_word, ptx::kErrWaitFull);
+        if (jb == 0) ptx::mbar_wait(&b_full[sb], b_par, abort_flag, p.err_word, ptx::kErrWaitFull);
         if (p.trace && lane == 0) stamp(p, 1, ti);
-        ptx::mbar_wait(&a_full[sa], (t / kAStages) & 1, abort_flag, p.err_word, ptx::kErrWaitConv);
+        ptx::mbar_wait(&a_full[sa], a_par, abort_flag, p.err_word, ptx::kErrWaitConv);
         if (p.trace && lane == 0) stamp(p, 1, ti);
         const bool last_in_block = (in_blk + 1 == p.tiles_per_block) || (t == my_tiles - 1);
-        const uint32_t a_lo = a_lo0 + (uint32_t)sa * (kABytes >> 4);
-        const uint32_t b_lo = b_lo0 + (uint32_t)(sb * kBGroup + jb) * (kBBytes >> 4);
         const uint32_t d_tmem = tmem_base + buf * MP;
 #pragma unroll
         for (int k = 0; k < BK / UMMA_K; ++k) {
@@ -336,13 +337,31 @@ __global__ void __launch_bounds__(kThreads, 1)
           ptx::mma_f16_ss_pred(d_tmem, ad, bd, idesc, (in_blk | k) != 0 ? 1u : 0u, leader);
         }
         ptx::mma_commit_pred(&a_empty[sa], leader);
-        if (jb == kBGroup - 1 || t == my_tiles - 1) ptx::mma_commit_pred(&b_empty[sb], leader);
+        const bool group_done = (jb == kBGroup - 1) || (t == my_tiles - 1);
+        if (group_done) ptx::mma_commit_pred(&b_empty[sb], leader);
         if (last_in_block) ptx::mma_commit_pred(&acc_full[buf], leader);
         if (p.trace && lane == 0) stamp(p, 1, ti);
         ++in_blk;
         if (last_in_block) {
           in_blk = 0;
           ++blk;
+        }
+        // next operand slot
+        a_lo += kABytes >> 4;
+        if (++sa == kAStages) {
+          sa = 0;
+          a_par ^= 1;
+          a_lo = a_lo0;
+        }
+        // next activation tile
+        b_lo += kBBytes >> 4;
+        if (++jb == kBGroup) {
+          jb = 0;
+          if (++sb == kBStages) {
+            sb = 0;
+            b_par ^= 1;
+            b_lo = b_lo0;
+          }
         }
       }
     }
