@@ -157,6 +157,9 @@ __global__ void __launch_bounds__(kThreads)
                               int saturate) {
   __shared__ uint32_t s_red[kThreads / 32];
   __shared__ int s_isum[kThreads / 32];
+  // the GEMM that consumes this kernel's output may start its set-up now; it waits for this grid to finish
+  // (griddepcontrol.wait) before it reads anything
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int64_t m = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nvec = (int)(K >> 3);  // 16-byte chunks (8 bf16) in the row

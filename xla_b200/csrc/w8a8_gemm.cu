@@ -110,6 +110,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   ptx::tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Programmatic dependent launch: everything above (barriers, TMEM allocation, descriptor prefetch) may run
+  // while the kernel that produces the quantized activations drains; its results are only touched below.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -349,7 +352,21 @@ int launch_w8a8_tc(const int8_t* xq, const int8_t* w, const float* w_scale, cons
   p.err_word = device_error_word();
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  w8a8_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(map_x, map_w, map_out, p);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t le = cudaLaunchKernelEx(&cfg, w8a8_tc_kernel, map_x, map_w, map_out, p);
+  if (le != cudaSuccess) {
+    cudaGetLastError();
+    return fail(QMM_ERR_LAUNCH, "w8a8_tc_kernel launch: %s", cudaGetErrorString(le));
+  }
   return check_launch("w8a8_tc_kernel");
 }
 
