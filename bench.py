@@ -337,6 +337,13 @@ def tp_mlp_times(dev, stream, g, world, rank, peaks, Ms=(1, 64, 512)):
   op = torch.ops.xla_b200.quantized_matmul_packed
   res = {}
   gu = None
+  peers = None
+  if world > 1:
+    try:
+      from xla_b200 import peer_reduce
+      peers = peer_reduce.PeerAllReduce(max_elems=32 * hl)
+    except Exception as e:
+      print(f"[bench] peer-memory all-reduce unavailable ({type(e).__name__}: {e})", file=sys.stderr)
   for M in Ms:
     x = torch.randn(M, H, generator=g, device=dev).bfloat16()
 
@@ -396,6 +403,26 @@ def tp_mlp_times(dev, stream, g, world, rank, peaks, Ms=(1, 64, 512)):
         res[f"M{M}"]["us_per_mlp_fused_gate_up"] = usf
       except Exception as e:
         res[f"M{M}"]["us_per_mlp_fused_gate_up"] = f"not measured ({type(e).__name__})"
+      if world > 1 and peers is not None and peers.fits(M, hl):
+        # and with the down projection's partial results summed by the one-shot peer-memory kernel
+        from xla_b200 import packed as _packed
+
+        def mlp_peer(i):
+          h = torch.ops.xla_b200.quantized_gate_up(x, gu[0], gu[1], block_size=BS, int4_weight=True, weight_is_packed=True,
+                                                   out_dtype=torch.bfloat16)
+          _packed.quantized_matmul_packed(h, down_w, down_s, block_size=BS, int4_weight=True, weight_is_packed=True,
+                                          out_dtype=torch.float32, out=peers.partial_view(M, hl))
+          return peers.reduce(M, hl, torch.bfloat16)
+
+        try:
+          usp = time_graph(mlp_peer, stream, reps=4, iters=3)
+          t = torch.tensor([usp], dtype=torch.float64, device=dev)
+          dist.all_reduce(t, op=dist.ReduceOp.MAX)
+          res[f"M{M}"]["us_per_mlp_fused_gate_up_peer_allreduce"] = float(t.item())
+        except Exception as e:
+          res[f"M{M}"]["us_per_mlp_fused_gate_up_peer_allreduce"] = f"not measured ({type(e).__name__}: {e})"
+  if peers is not None:
+    peers.close()
   return res
 
 

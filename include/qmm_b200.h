@@ -223,6 +223,36 @@ QMM_API int qmm_pack_int4_sbn(const int8_t* w, uint8_t* wp, int64_t S, int64_t b
 QMM_API int qmm_unpack_int4_nk(const uint8_t* wp, int8_t* w, int64_t N, int64_t K, void* stream);
 
 /*
+ * Peer-memory buffers and a one-shot all-reduce for the row-parallel (K-sharded) linear on the GPUs of one box.
+ * No reference counterpart as code: the reference leaves the all-reduce after a K-sharded matmul to XLA
+ * (torch_xla/csrc/cross_replica_reduces.cpp:154; sharding by torch_xla/distributed/spmd/xla_sharding.py:685).
+ *
+ *   qmm_peer_buffer_create   cudaMalloc's `bytes` on the current device (zero-filled) and returns the pointer
+ *                            and a 64-byte CUDA IPC handle for it.  This is the one place the library allocates:
+ *                            IPC handles need a whole allocation of their own.
+ *   qmm_peer_buffer_open     maps a peer's buffer (its handle, received over any channel) into this process with
+ *                            peer access enabled; qmm_peer_buffer_close unmaps it; qmm_peer_buffer_destroy frees
+ *                            one's own buffer (after every peer has closed it).
+ *   qmm_allreduce_oneshot    out[i] = sum_r data_ptrs[r][i] (fp32 partials, summed in rank order, converted to
+ *                            out_dtype), i < count, count % 4 == 0.  data_ptrs / flag_ptrs are HOST arrays of
+ *                            `world` device pointers, entry `rank` being this process's own buffers, the others
+ *                            peer mappings; flag_ptrs[r] points to 16 zero-initialised uint32 on rank r.  `epoch`
+ *                            must increase by one per call, starting at 1, identically on every rank; 0 makes
+ *                            the kernel keep the call number itself in flag word 8 (what a launch captured in a
+ *                            CUDA graph needs, since its arguments are frozen).  Callers
+ *                            alternate between two data regions so that a rank may write call e+1's partial while
+ *                            a peer still reads call e's.  Every rank must launch the call (one kernel per GPU,
+ *                            the kernels wait for one another through the flags, at most ~1 s: on expiry the
+ *                            device error word is set and nothing is reduced).  world <= 8.
+ */
+QMM_API int qmm_peer_buffer_create(size_t bytes, void** ptr, unsigned char handle[64]);
+QMM_API int qmm_peer_buffer_open(const unsigned char handle[64], void** ptr);
+QMM_API int qmm_peer_buffer_close(void* ptr);
+QMM_API int qmm_peer_buffer_destroy(void* ptr);
+QMM_API int qmm_allreduce_oneshot(void* const* data_ptrs, void* const* flag_ptrs, int rank, int world, uint32_t epoch,
+                          void* out, int out_dtype, int64_t count, void* stream);
+
+/*
  * Device-side error word of the current device.  Kernels that wait on hardware barriers give up
  * after a bounded number of polls and record a non-zero code here instead of hanging.
  * Reads the word back (this call synchronises `stream`), stores it in *flag (HOST pointer) and

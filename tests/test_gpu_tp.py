@@ -32,9 +32,12 @@ def _worker(rank, world, port, results):
     import xla_b200
     from oracle import qmm_oracle as qo
     from xla_b200 import tensor_parallel as tp
+    from xla_b200 import _capi, peer_reduce
+    import ctypes
     g = torch.Generator().manual_seed(0)  # same seed on every rank: identical full tensors
     H, F, bs = 1024, 2048, 128
     ok = True
+    peers = peer_reduce.PeerAllReduce(max_elems=64 * H)
     for M in (1, 8, 64):
       x = torch.randn(M, H, generator=g).bfloat16()
       w_up = torch.randint(-8, 8, (F, H), generator=g, dtype=torch.int8)
@@ -56,9 +59,24 @@ def _worker(rank, world, port, results):
                   out_dtype=torch.bfloat16)
       ok &= torch.equal(h_local, h_full[:, rank * F // world:(rank + 1) * F // world])
       ok &= qo.max_abs_rel(y, y_full) < 1e-2
+      # the same row-parallel linear with the one-shot peer-memory all-reduce, twice (both buffer slots)
+      row_p = tp.RowParallelQuantizedLinear(wp_dn, s_dn.to(dev), block_size=bs, int4_weight=True, weight_is_packed=True,
+                                            out_dtype=torch.bfloat16, peer_reduce=peers)
+      for _ in range(2):
+        y_p = row_p(h_local)
+        ok &= y_p.shape == y.shape and y_p.dtype == y.dtype
+        ok &= qo.max_abs_rel(y_p, y_full) < 1e-2
+        ok &= qo.max_abs_rel(y_p, y) < 1e-2
+      # every rank summed the same partials in the same order: identical bits everywhere
+      gathered = [torch.empty_like(y_p) for _ in range(world)]
+      dist.all_gather(gathered, y_p)
+      ok &= all(torch.equal(t, gathered[0]) for t in gathered)
       # and the oracle for the first linear
       exact = qo.quantized_matmul(x.float(), qo.nk_to_sbn(w_up, bs), s_up, block_size=bs, dot_round=None)
       ok &= qo.max_abs_rel(col(x.to(dev), gather=True), exact) < 1e-2
+    flag = ctypes.c_uint32(7)
+    ok &= _capi.lib().qmm_device_error_flag(ctypes.byref(flag), _capi.stream_ptr(dev)) == 0 and flag.value == 0
+    peers.close()
     results[rank] = bool(ok)
   finally:
     dist.destroy_process_group()

@@ -29,6 +29,12 @@ SIGNATURES = {
     "qmm_w8a16_perchannel": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i, _p]),
     "qmm_w4a16_perchannel_packed": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i, _p]),
     "qmm_w8a16_blockwise": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _p]),
+    "qmm_peer_buffer_create": (_i, [_sz, ctypes.POINTER(ctypes.c_void_p), ctypes.c_char_p]),
+    "qmm_peer_buffer_open": (_i, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]),
+    "qmm_peer_buffer_close": (_i, [_p]),
+    "qmm_peer_buffer_destroy": (_i, [_p]),
+    "qmm_allreduce_oneshot": (_i, [ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p), _i, _i, ctypes.c_uint32,
+                                  _p, _i, _i64, _p]),
     "qmm_gate_up_decode": (_i, [_i, _p, _i, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _p]),
     "qmm_blockwise_sbn": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _p]),
     "qmm_w4a16_blockwise_packed": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _p]),

@@ -454,6 +454,66 @@ int qmm_unpack_int4_nk(const uint8_t* wp, int8_t* w, int64_t N, int64_t K, void*
   return launch_unpack_int4_nk(wp, w, N, K, as_stream(stream));
 }
 
+int qmm_peer_buffer_create(size_t bytes, void** ptr, unsigned char handle[64]) {
+  if (!ptr || !handle) return fail(QMM_ERR_NULL, "peer_buffer_create: null pointer");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes ? bytes : 16);
+  if (e == cudaSuccess) e = cudaMemset(p, 0, bytes ? bytes : 16);
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    if (p) cudaFree(p);
+    cudaGetLastError();
+    return fail(QMM_ERR_DEVICE, "peer_buffer_create: %s", cudaGetErrorString(e));
+  }
+  memcpy(handle, &h, 64);
+  *ptr = p;
+  return QMM_OK;
+}
+
+int qmm_peer_buffer_open(const unsigned char handle[64], void** ptr) {
+  if (!ptr || !handle) return fail(QMM_ERR_NULL, "peer_buffer_open: null pointer");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(QMM_ERR_DEVICE, "peer_buffer_open: %s", cudaGetErrorString(e));
+  }
+  *ptr = p;
+  return QMM_OK;
+}
+
+int qmm_peer_buffer_close(void* ptr) {
+  if (!ptr) return QMM_OK;
+  cudaError_t e = cudaIpcCloseMemHandle(ptr);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(QMM_ERR_DEVICE, "peer_buffer_close: %s", cudaGetErrorString(e));
+  }
+  return QMM_OK;
+}
+
+int qmm_peer_buffer_destroy(void* ptr) {
+  if (!ptr) return QMM_OK;
+  cudaError_t e = cudaFree(ptr);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(QMM_ERR_DEVICE, "peer_buffer_destroy: %s", cudaGetErrorString(e));
+  }
+  return QMM_OK;
+}
+
+int qmm_allreduce_oneshot(void* const* data_ptrs, void* const* flag_ptrs, int rank, int world, uint32_t epoch, void* out,
+                          int out_dtype, int64_t count, void* stream) {
+  if (!data_ptrs || !flag_ptrs || !out) return fail(QMM_ERR_NULL, "allreduce_oneshot: null pointer");
+  if (out_dtype != QMM_F32 && out_dtype != QMM_BF16 && out_dtype != QMM_F16)
+    return fail(QMM_ERR_BAD_SHAPE, "allreduce_oneshot: bad out_dtype %d", out_dtype);
+  return launch_peer_allreduce(data_ptrs, flag_ptrs, rank, world, epoch, out, out_dtype, count, as_stream(stream));
+}
+
 int qmm_device_error_flag(uint32_t* flag, void* stream) {
   if (!flag) return fail(QMM_ERR_NULL, "flag is NULL");
   uint32_t* word = device_error_word();

@@ -60,6 +60,11 @@ bool decode_tc_supported(int wbits, int64_t M, int64_t N, int64_t K, int64_t blo
 int launch_decode_tc(int wbits, const void* x, int x_dt, const void* w, const float* scale, void* out, int out_dt,
                      int64_t M, int64_t N, int64_t K, int64_t block_size, cudaStream_t st);
 
+// ---- peer_reduce.cu -----------------------------------------------------------------------
+// One-shot all-reduce of fp32 partial results that every rank keeps in peer-mapped memory.
+int launch_peer_allreduce(void* const* data_ptrs, void* const* flag_ptrs, int rank, int world, uint32_t epoch, void* out,
+                          int out_dt, int64_t count, cudaStream_t st);
+
 // ---- act_quant.cu -------------------------------------------------------------------------
 int launch_quantize_activation(const void* x, int x_dt, int8_t* xq, float* x_scale,
                                int32_t* rowsum, int64_t M, int64_t K, int saturate,

@@ -92,7 +92,9 @@ def _shapes(x, w, scaler, zero_point, block_size, weight_is_packed):
 
 
 def quantized_matmul_packed(x, w, scaler, zero_point=None, block_size=-1, int4_weight=False,
-                            weight_is_packed=False, quantize_activation=False, out_dtype=None):
+                            weight_is_packed=False, quantize_activation=False, out_dtype=None, out=None):
+  """CUDA kernel of ``torch.ops.xla_b200.quantized_matmul_packed``.  ``out`` (Python callers only, not part of
+  the operator schema) is a preallocated contiguous [M, N] result buffer, e.g. a peer-mapped one."""
   _capi.require_cuda(x, w, scaler, zero_point)
   N, K = _shapes(x, w, scaler, zero_point, block_size, weight_is_packed)
   if block_size != -1:
@@ -107,6 +109,7 @@ def quantized_matmul_packed(x, w, scaler, zero_point=None, block_size=-1, int4_w
   L = _capi.lib()
   variant = _capi.VARIANTS[_qm._variant]
   zp_after = not quantize_activation and _qm._zero_point_outside(M, x2, zero_point)
+  out_buf = None if quantize_activation else out
 
   def run():
     if quantize_activation:
@@ -114,7 +117,11 @@ def quantized_matmul_packed(x, w, scaler, zero_point=None, block_size=-1, int4_w
         raise NotImplementedError("W4A8 (packed int4 weights with activation quantization) is not supported")
       return _qm._w8a8(x2, w, s32, zp32, out_dtype)
     kdt = torch.float32 if zp_after else out_dtype
-    out = torch.empty((M, N), dtype=kdt, device=x.device)
+    if out_buf is not None and not zp_after:
+      assert out_buf.shape == (M, N) and out_buf.dtype == kdt and out_buf.is_contiguous() and out_buf.device == x.device
+      out = out_buf
+    else:
+      out = torch.empty((M, N), dtype=kdt, device=x.device)
     st = _capi.stream_ptr(x.device)
     args = (x2.data_ptr(), _capi.dtype_code(x2.dtype), w.data_ptr(), s32.data_ptr(),
             None if zp_after else _capi.ptr(zp32), out.data_ptr(), _capi.dtype_code(kdt), M, N, K)
@@ -130,6 +137,8 @@ def quantized_matmul_packed(x, w, scaler, zero_point=None, block_size=-1, int4_w
         _capi.check(L.qmm_w8a16_blockwise(*args, block_size, variant, st))
     if zp_after:
       out = _qm._subtract_zero_point(out, x2, zp32, block_size).to(out_dtype)
+      if out_buf is not None:
+        out = out_buf.copy_(out)
     return out
 
   out = _capi.on_device(x.device, run)

@@ -24,10 +24,10 @@ def _world(group=None):
   return 0, 1
 
 
-def _default_local_op(x, w, scaler, zero_point, block_size, int4_weight, weight_is_packed, out_dtype):
+def _default_local_op(x, w, scaler, zero_point, block_size, int4_weight, weight_is_packed, out_dtype, out=None):
   from . import packed
   return packed.quantized_matmul_packed(x, w, scaler, zero_point, block_size=block_size, int4_weight=int4_weight,
-                                        weight_is_packed=weight_is_packed, out_dtype=out_dtype)
+                                        weight_is_packed=weight_is_packed, out_dtype=out_dtype, out=out)
 
 
 def shard_column(w, scaler, zero_point, rank, world, block_size=-1):
@@ -90,9 +90,13 @@ class RowParallelQuantizedLinear(torch.nn.Module):
   """out = all_reduce_sum_r quantized_matmul(x[:, K slice r], local weight)."""
 
   def __init__(self, w, scaler, zero_point=None, in_features=None, block_size=-1, int4_weight=False,
-               weight_is_packed=False, out_dtype=None, reduce_dtype=torch.float32, group=None, local_op=None):
+               weight_is_packed=False, out_dtype=None, reduce_dtype=torch.float32, group=None, local_op=None,
+               peer_reduce=None):
     super().__init__()
     self.group = group
+    # a xla_b200.peer_reduce.PeerAllReduce: results that fit its buffers are summed by the one-shot
+    # peer-memory kernel instead of the process group's all-reduce
+    self.peer_reduce = peer_reduce
     rank, world = _world(group)
     k = in_features if in_features is not None else (w.shape[1] * (2 if weight_is_packed else 1))
     wl, sl, zl = shard_row(w, scaler, zero_point, rank, world, k, block_size, weight_is_packed)
@@ -114,6 +118,15 @@ class RowParallelQuantizedLinear(torch.nn.Module):
 
   def forward(self, x_local):
     _, world = _world(self.group)
+    pr = self.peer_reduce
+    if pr is not None and world > 1 and self.local_op is _default_local_op:
+      M = x_local.numel() // x_local.shape[-1]
+      N = self.weight.shape[0]
+      if pr.fits(M, N):
+        out_dtype = self.out_dtype if self.out_dtype is not None else torch.float32
+        self.local_op(x_local.reshape(M, -1), self.weight, self.weight_scaler, self.zero_point, self.block_size,
+                      self.int4_weight, self.weight_is_packed, torch.float32, out=pr.partial_view(M, N))
+        return pr.reduce(M, N, out_dtype).reshape(x_local.shape[:-1] + (N,))
     part_dtype = self.reduce_dtype if world > 1 else self.out_dtype
     y = self.local_op(x_local, self.weight, self.weight_scaler, self.zero_point, self.block_size, self.int4_weight,
                       self.weight_is_packed, part_dtype)
