@@ -337,11 +337,12 @@ def tp_mlp_times(dev, stream, g, world, rank, peaks, Ms=(1, 64, 512)):
   op = torch.ops.xla_b200.quantized_matmul_packed
   res = {}
   gu = None
-  peers = None
+  peers = fused = None
   if world > 1:
     try:
       from xla_b200 import peer_reduce
       peers = peer_reduce.PeerAllReduce(max_elems=32 * hl)
+      fused = peer_reduce.FusedRowParallelDecode(N=hl, max_M=8)
     except Exception as e:
       print(f"[bench] peer-memory all-reduce unavailable ({type(e).__name__}: {e})", file=sys.stderr)
   for M in Ms:
@@ -421,8 +422,24 @@ def tp_mlp_times(dev, stream, g, world, rank, peaks, Ms=(1, 64, 512)):
           res[f"M{M}"]["us_per_mlp_fused_gate_up_peer_allreduce"] = float(t.item())
         except Exception as e:
           res[f"M{M}"]["us_per_mlp_fused_gate_up_peer_allreduce"] = f"not measured ({type(e).__name__}: {e})"
+      if world > 1 and fused is not None and fused.fits(M, hl):
+        # two kernels per MLP: gate+up+silu, then the down projection whose epilogue also sums over the ranks
+        def mlp_two(i):
+          h = torch.ops.xla_b200.quantized_gate_up(x, gu[0], gu[1], block_size=BS, int4_weight=True, weight_is_packed=True,
+                                                   out_dtype=torch.bfloat16)
+          return fused(h, down_w, down_s, block_size=BS, weight_is_packed=True, out_dtype=torch.bfloat16)
+
+        try:
+          us2 = time_graph(mlp_two, stream, reps=4, iters=3)
+          t = torch.tensor([us2], dtype=torch.float64, device=dev)
+          dist.all_reduce(t, op=dist.ReduceOp.MAX)
+          res[f"M{M}"]["us_per_mlp_fused_gate_up_fused_allreduce"] = float(t.item())
+        except Exception as e:
+          res[f"M{M}"]["us_per_mlp_fused_gate_up_fused_allreduce"] = f"not measured ({type(e).__name__}: {e})"
   if peers is not None:
     peers.close()
+  if fused is not None:
+    fused.close()
   return res
 
 

@@ -253,6 +253,27 @@ QMM_API int qmm_allreduce_oneshot(void* const* data_ptrs, void* const* flag_ptrs
                           void* out, int out_dtype, int64_t count, void* stream);
 
 /*
+ * Row-parallel (K-sharded) decode linear with the sum over ranks fused into the kernel: every CTA writes its
+ * 16 x M partial sums into this rank's exchange buffer, flags the tile on every peer, waits (bounded, ~1 s, then the
+ * device error word is set) for the same tile of every peer and stores the sum of the `world` partials, added in
+ * rank order in fp32 - all ranks end up with bit-identical results and no separate all-reduce runs.
+ *   out[m,n] = sum_r sum_b scale_r[b,n] * (sum_{k in block b of rank r's K slice} x_r[m,k] * w_r[n,k])
+ * x, w, scale are THIS rank's slices (wbits 4: packed uint8 [N,K/2]; 8: int8 [N,K]; block_size 0 = per-channel
+ * scale [N], which every rank applies to its partial).  1 <= M <= 8, bf16/f16 activations.
+ * peer_bufs: HOST array of `world` device pointers to exchange buffers of qmm_rowparallel_buffer_bytes(max_M, N,
+ * world) bytes each, created zero-filled with qmm_peer_buffer_create on their owners and mapped with
+ * qmm_peer_buffer_open elsewhere; slot_floats = max_M * N as passed there.  Every rank must make the same calls in
+ * the same order on such a buffer set; a set serves one N.  The call number lives in the buffer, so a launch
+ * captured in a CUDA graph stays valid on replay.
+ * Replaces: nothing in the reference as code - the K-sharded matmul plus the all-reduce XLA would insert after it
+ * (torch_xla/csrc/cross_replica_reduces.cpp:154), per projection the formula of xla_quantized_matmul.py:152-170.
+ */
+QMM_API size_t qmm_rowparallel_buffer_bytes(int64_t max_M, int64_t N, int world);
+QMM_API int qmm_rowparallel_decode(int wbits, const void* x, int x_dtype, const void* w, const float* scale, void* out,
+                           int out_dtype, int64_t M, int64_t N, int64_t K, int64_t block_size,
+                           void* const* peer_bufs, int rank, int world, int64_t slot_floats, void* stream);
+
+/*
  * Device-side error word of the current device.  Kernels that wait on hardware barriers give up
  * after a bounded number of polls and record a non-zero code here instead of hanging.
  * Reads the word back (this call synchronises `stream`), stores it in *flag (HOST pointer) and

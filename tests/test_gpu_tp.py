@@ -38,6 +38,7 @@ def _worker(rank, world, port, results):
     H, F, bs = 1024, 2048, 128
     ok = True
     peers = peer_reduce.PeerAllReduce(max_elems=64 * H)
+    fused = peer_reduce.FusedRowParallelDecode(N=H, max_M=8)
     for M in (1, 8, 64):
       x = torch.randn(M, H, generator=g).bfloat16()
       w_up = torch.randint(-8, 8, (F, H), generator=g, dtype=torch.int8)
@@ -71,12 +72,24 @@ def _worker(rank, world, port, results):
       gathered = [torch.empty_like(y_p) for _ in range(world)]
       dist.all_gather(gathered, y_p)
       ok &= all(torch.equal(t, gathered[0]) for t in gathered)
+      if M <= 8:
+        # and with the exchange fused into the decode kernel itself, three calls (both slots, counter wrap of the slots)
+        row_f = tp.RowParallelQuantizedLinear(wp_dn, s_dn.to(dev), block_size=bs, int4_weight=True, weight_is_packed=True,
+                                              out_dtype=torch.bfloat16, fused_decode=fused)
+        for _ in range(3):
+          y_f = row_f(h_local)
+          ok &= y_f.shape == y.shape and y_f.dtype == y.dtype
+          ok &= torch.equal(y_f, y_p)  # same partials, same order of addition, same rounding
+        gathered = [torch.empty_like(y_f) for _ in range(world)]
+        dist.all_gather(gathered, y_f)
+        ok &= all(torch.equal(t, gathered[0]) for t in gathered)
       # and the oracle for the first linear
       exact = qo.quantized_matmul(x.float(), qo.nk_to_sbn(w_up, bs), s_up, block_size=bs, dot_round=None)
       ok &= qo.max_abs_rel(col(x.to(dev), gather=True), exact) < 1e-2
     flag = ctypes.c_uint32(7)
     ok &= _capi.lib().qmm_device_error_flag(ctypes.byref(flag), _capi.stream_ptr(dev)) == 0 and flag.value == 0
     peers.close()
+    fused.close()
     results[rank] = bool(ok)
   finally:
     dist.destroy_process_group()

@@ -35,6 +35,9 @@ SIGNATURES = {
     "qmm_peer_buffer_destroy": (_i, [_p]),
     "qmm_allreduce_oneshot": (_i, [ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p), _i, _i, ctypes.c_uint32,
                                   _p, _i, _i64, _p]),
+    "qmm_rowparallel_buffer_bytes": (_sz, [_i64, _i64, _i]),
+    "qmm_rowparallel_decode": (_i, [_i, _p, _i, _p, _p, _p, _i, _i64, _i64, _i64, _i64, ctypes.POINTER(ctypes.c_void_p), _i, _i,
+                                   _i64, _p]),
     "qmm_gate_up_decode": (_i, [_i, _p, _i, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _p]),
     "qmm_blockwise_sbn": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _p]),
     "qmm_w4a16_blockwise_packed": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _p]),

@@ -514,6 +514,30 @@ int qmm_allreduce_oneshot(void* const* data_ptrs, void* const* flag_ptrs, int ra
   return launch_peer_allreduce(data_ptrs, flag_ptrs, rank, world, epoch, out, out_dtype, count, as_stream(stream));
 }
 
+size_t qmm_rowparallel_buffer_bytes(int64_t max_M, int64_t N, int world) {
+  if (max_M < 1 || N < 1 || world < 1) return 0;
+  const size_t data = 2 * (size_t)max_M * (size_t)N * sizeof(float);
+  const size_t flags = ((size_t)world * (size_t)((N + 15) / 16) + 2) * sizeof(uint32_t);
+  return (data + flags + 255) / 256 * 256;
+}
+
+int qmm_rowparallel_decode(int wbits, const void* x, int x_dtype, const void* w, const float* scale, void* out,
+                           int out_dtype, int64_t M, int64_t N, int64_t K, int64_t block_size,
+                           void* const* peer_bufs, int rank, int world, int64_t slot_floats, void* stream) {
+  if (wbits != 4 && wbits != 8) return fail(QMM_ERR_BAD_SHAPE, "rowparallel_decode: wbits must be 4 or 8, got %d", wbits);
+  if (!x || !w || !scale || !out || !peer_bufs) return fail(QMM_ERR_NULL, "rowparallel_decode: null pointer");
+  if (M < 0 || N < 0 || K < 0) return fail(QMM_ERR_BAD_SHAPE, "rowparallel_decode: negative size");
+  if (block_size < 0 || (block_size > 0 && K % block_size != 0))
+    return fail(QMM_ERR_BAD_SHAPE, "rowparallel_decode: K (%lld) must be a multiple of block_size (%lld)", (long long)K,
+                (long long)block_size);
+  if (out_dtype != QMM_F32 && out_dtype != QMM_BF16 && out_dtype != QMM_F16)
+    return fail(QMM_ERR_BAD_SHAPE, "rowparallel_decode: bad out_dtype %d", out_dtype);
+  if (M == 0 || N == 0) return QMM_OK;
+  log_choice("rowparallel_decode", "mma", M, N, K);
+  return launch_decode_mma_allreduce(wbits, x, x_dtype, w, scale, out, out_dtype, M, N, K, block_size, peer_bufs, rank, world,
+                                     slot_floats, as_stream(stream));
+}
+
 int qmm_device_error_flag(uint32_t* flag, void* stream) {
   if (!flag) return fail(QMM_ERR_NULL, "flag is NULL");
   uint32_t* word = device_error_word();

@@ -111,15 +111,47 @@ __device__ __forceinline__ uint32_t sub_bias(uint32_t p, float bias) {
 __device__ __forceinline__ float silu_mul(float gate, float up) { return gate / (1.f + expf(-gate)) * up; }
 __device__ __forceinline__ int64_t gate_up_column(int64_t n) { return ((n >> 4) << 3) + (n & 7); }
 
+// Row-parallel exchange fused into the decode kernel (AR = true): the CTA's 16 x M partial sums go to this rank's
+// peer-visible buffer, the CTA tells every peer that ITS tile is there (one flag word per rank and tile, holding
+// the call number), waits - bounded - for the same tile from every peer and writes the sum of the G partials, added
+// in rank order.  Tiles are exchanged as they finish, so the waiting of one CTA overlaps the weight stream of the
+// others.  Buffer layout (per rank): two data slots of slot_floats fp32 (call e uses slot e & 1), then
+// world x tiles flag words, then the call counter and a ticket.  The call number is kept in device memory, so a
+// launch captured in a CUDA graph stays valid on replay; the previous call of the stream has completed before
+// this one signals (it waits on griddepcontrol.wait first), which is what makes two slots enough.
+constexpr int kArMaxRanks = 8;
+struct ArParams {
+  float* data[kArMaxRanks];      // base of every rank's buffer (index = rank); entry `rank` is this GPU's own
+  int rank, world;
+  uint32_t slot_floats;          // fp32 elements per data slot (>= M * N)
+  uint32_t tiles;                // CTAs of the launch = flag words per rank
+};
+__device__ __forceinline__ uint32_t* ar_flags(const ArParams& a, int owner) {
+  return reinterpret_cast<uint32_t*>(a.data[owner] + 2 * (size_t)a.slot_floats);
+}
+__device__ __forceinline__ void ar_st_release(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ar_ld_acquire(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float ar_ld_peer(const float* p) {
+  float v;
+  asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+
 // NT = number of 8-token tiles (M <= 8*NT); RG = 16-row groups per CTA (each warp converts RG groups per
 // step and reuses its activation registers for all of them); WARPS = warps splitting K.
 // One "fold" = the end of a scale block (blockwise) or of a single step (per-channel): the partial tile,
 // minus bias * sum(x), is added into the totals.
-template <int WBITS, typename XT, int NT, int RG, int WARPS>
+template <int WBITS, typename XT, int NT, int RG, int WARPS, bool AR = false>
 __global__ void __launch_bounds__(WARPS * 32)
     decode_mma_kernel(const XT* __restrict__ x, const uint8_t* __restrict__ w, const float* __restrict__ scale,
                       void* __restrict__ out, int out_dt, int M, int64_t N, int64_t K, int steps_per_block,
-                      int spb_shift, int blockwise, int gate_up) {
+                      int spb_shift, int blockwise, int gate_up, const ArParams ar, uint32_t* err_word) {
   constexpr int VPS = 512 / WBITS;      // values of one weight row per step: 128 (int4) or 64 (int8)
   constexpr int VPL = VPS / 4;          // values per lane per row per step: 32 or 16
   constexpr int XREGS = VPL / 2;        // packed activation pairs per lane per token tile: 16 or 8
@@ -323,6 +355,65 @@ __global__ void __launch_bounds__(WARPS * 32)
       s_part[warp][16 * r + g + 8][8 * i + 2 * t + 1] = total[r][i][3];
     }
   __syncthreads();
+  if constexpr (AR) {
+    // ---- fused row-parallel exchange ----
+    __shared__ uint32_t s_epoch;
+    __shared__ int s_ok;
+    uint32_t* my_flags = ar_flags(ar, ar.rank);
+    uint32_t* ctr = my_flags + (size_t)ar.world * ar.tiles;  // [0] call counter, [1] ticket
+    if (threadIdx.x == 0) s_epoch = *reinterpret_cast<volatile uint32_t*>(ctr) + 1u;
+    __syncthreads();
+    const uint32_t epoch = s_epoch;
+    float* own = ar.data[ar.rank] + (size_t)(epoch & 1u) * ar.slot_floats;
+    for (int idx = threadIdx.x; idx < ROWS * NT * 8; idx += WARPS * 32) {
+      const int row = idx % ROWS, tok = idx / ROWS;
+      const int64_t n = n0 + row;
+      if (n < N && tok < M) {
+        float v = 0.f;
+#pragma unroll
+        for (int wi = 0; wi < WARPS; ++wi) v += s_part[wi][row][tok];
+        if (!blockwise) v *= __ldg(scale + n);
+        own[(int64_t)tok * N + n] = v;
+      }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < ar.world)
+      ar_st_release(ar_flags(ar, threadIdx.x) + (size_t)ar.rank * ar.tiles + blockIdx.x, epoch);
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (threadIdx.x < ar.world) {
+      const uint32_t* f = my_flags + (size_t)threadIdx.x * ar.tiles + blockIdx.x;
+      const long long t0 = clock64();
+      uint32_t spins = 0;
+      while ((int32_t)(ar_ld_acquire(f) - epoch) < 0) {
+        if ((++spins & 0x3ff) == 0 && clock64() - t0 > 2000000000ll) {  // about a second: give up, report
+          s_ok = 0;
+          if (err_word) atomicCAS(err_word, 0u, 8u | ((uint32_t)threadIdx.x << 8));
+          break;
+        }
+      }
+    }
+    __syncthreads();
+    if (s_ok) {
+      for (int idx = threadIdx.x; idx < ROWS * NT * 8; idx += WARPS * 32) {
+        const int row = idx % ROWS, tok = idx / ROWS;
+        const int64_t n = n0 + row;
+        if (n < N && tok < M) {
+          const int64_t o = (int64_t)tok * N + n;
+          float v = 0.f;
+          for (int r = 0; r < ar.world; ++r) v += ar_ld_peer(ar.data[r] + (size_t)(epoch & 1u) * ar.slot_floats + o);
+          store_from_f32(out, o, out_dt, v);
+        }
+      }
+    }
+    // the CTA that finishes last advances the call counter (every CTA has read it by then)
+    if (threadIdx.x == 0 && atomicAdd(ctr + 1, 1u) == gridDim.x - 1) {
+      ctr[1] = 0;
+      *reinterpret_cast<volatile uint32_t*>(ctr) = epoch;
+    }
+    return;
+  }
   for (int idx = threadIdx.x; idx < ROWS * NT * 8; idx += WARPS * 32) {
     const int row = idx % ROWS, tok = idx / ROWS;  // consecutive threads -> consecutive n
     const int64_t n = n0 + row;
@@ -679,7 +770,7 @@ cudaError_t launch_staged(const XT* xp, const uint8_t* wp, const float* scale, v
 
 template <int WBITS, typename XT>
 int launch_nt(const void* x, const void* w, const float* scale, void* out, int out_dt, int64_t M, int64_t N,
-              int64_t K, int64_t block_size, int gate_up, cudaStream_t st) {
+              int64_t K, int64_t block_size, int gate_up, cudaStream_t st, const ArParams* ar = nullptr) {
   constexpr int VPS = 512 / WBITS;
   const int spb = block_size > 0 ? (int)(block_size / VPS) : 1;
   int shift = -1;
@@ -692,11 +783,17 @@ int launch_nt(const void* x, const void* w, const float* scale, void* out, int o
   const uint8_t* wp = reinterpret_cast<const uint8_t*>(w);
 #define QMM_DECODE_LAUNCH(NT, RG, WARPS)                                                                        \
   launch_pdl(decode_mma_kernel<WBITS, XT, NT, RG, WARPS>, (unsigned)ceil_div(N, 16 * RG), WARPS * 32, 0, st, xp, wp, \
-             scale, out, out_dt, (int)M, N, K, spb, shift, bw, gate_up)
+             scale, out, out_dt, (int)M, N, K, spb, shift, bw, gate_up, ArParams{}, (uint32_t*)nullptr)
   // one token tile: many small CTAs, activations through L1 (64 KB for 8 tokens of 4096);
   // two or four tiles: one CTA per SM with the activations staged in shared memory
   cudaError_t err;
-  if (M <= 8)
+  if (ar) {
+    if (M > 8 || gate_up) return fail(QMM_ERR_UNSUPPORTED, "fused row-parallel exchange: M <= 8 only (got %lld)", (long long)M);
+    ArParams a = *ar;
+    a.tiles = (uint32_t)ceil_div(N, 16);
+    err = launch_pdl(decode_mma_kernel<WBITS, XT, 1, 1, 4, true>, (unsigned)ceil_div(N, 16), 128, 0, st, xp, wp, scale, out,
+                     out_dt, (int)M, N, K, spb, shift, bw, 0, a, device_error_word());
+  } else if (M <= 8)
     err = QMM_DECODE_LAUNCH(1, 1, 4);
   else if (M <= 16)
     err = launch_staged<WBITS, XT, 2>(xp, wp, scale, out, out_dt, M, N, K, spb, shift, bw, gate_up, st);
@@ -711,6 +808,31 @@ int launch_nt(const void* x, const void* w, const float* scale, void* out, int o
 }
 
 }  // namespace
+
+int launch_decode_mma_allreduce(int wbits, const void* x, int x_dt, const void* w, const float* scale, void* out, int out_dt,
+                                int64_t M, int64_t N, int64_t K, int64_t block_size, void* const* peer_bufs, int rank,
+                                int world, int64_t slot_floats, cudaStream_t st) {
+  if (world < 1 || world > kArMaxRanks || rank < 0 || rank >= world)
+    return fail(QMM_ERR_BAD_SHAPE, "fused row-parallel exchange: rank %d of %d (at most %d ranks)", rank, world, kArMaxRanks);
+  if (M > 8 || !decode_mma_supported(wbits, M, N, K, block_size, x, x_dt, w, false))
+    return fail(QMM_ERR_UNSUPPORTED, "fused row-parallel exchange: needs 1<=M<=8, bf16/f16 activations, K a multiple of %d "
+                "(M=%lld N=%lld K=%lld bs=%lld)", 512 / wbits, (long long)M, (long long)N, (long long)K, (long long)block_size);
+  if (slot_floats < M * N || slot_floats > 0xffffffffLL) return fail(QMM_ERR_WORKSPACE, "fused row-parallel exchange: data slot too small");
+  ArParams a = {};
+  for (int r = 0; r < world; ++r) {
+    if (!peer_bufs[r]) return fail(QMM_ERR_NULL, "fused row-parallel exchange: null buffer of rank %d", r);
+    a.data[r] = reinterpret_cast<float*>(peer_bufs[r]);
+  }
+  a.rank = rank;
+  a.world = world;
+  a.slot_floats = (uint32_t)slot_floats;
+  if (wbits == 4) {
+    if (x_dt == QMM_BF16) return launch_nt<4, __nv_bfloat16>(x, w, scale, out, out_dt, M, N, K, block_size, 0, st, &a);
+    return launch_nt<4, __half>(x, w, scale, out, out_dt, M, N, K, block_size, 0, st, &a);
+  }
+  if (x_dt == QMM_BF16) return launch_nt<8, __nv_bfloat16>(x, w, scale, out, out_dt, M, N, K, block_size, 0, st, &a);
+  return launch_nt<8, __half>(x, w, scale, out, out_dt, M, N, K, block_size, 0, st, &a);
+}
 
 bool decode_mma_supported(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size, const void* x, int x_dt,
                           const void* w, bool has_zp) {

@@ -52,6 +52,13 @@ bool decode_mma_supported(int wbits, int64_t M, int64_t N, int64_t K, int64_t bl
 int launch_decode_mma(int wbits, const void* x, int x_dt, const void* w, const float* scale, void* out, int out_dt,
                       int64_t M, int64_t N, int64_t K, int64_t block_size, cudaStream_t st, int gate_up = 0);
 
+// The same kernel for the K-sharded (row-parallel) linear with the sum over ranks fused into its epilogue:
+// peer_bufs[r] is rank r's exchange buffer (entry `rank` this GPU's own, the others peer mappings), each laid
+// out as two fp32 data slots of slot_floats elements, world * ceil(N/16) flag words, a call counter and a ticket.
+int launch_decode_mma_allreduce(int wbits, const void* x, int x_dt, const void* w, const float* scale, void* out, int out_dt,
+                                int64_t M, int64_t N, int64_t K, int64_t block_size, void* const* peer_bufs, int rank,
+                                int world, int64_t slot_floats, cudaStream_t st);
+
 // ---- decode_tc.cu -------------------------------------------------------------------------
 // Decode kernel on tcgen05 with the weight operand written to tensor memory (M <= 32, bf16/f16
 // activations, no zero point), K split over a thread-block cluster.

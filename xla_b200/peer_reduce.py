@@ -24,6 +24,71 @@ class _Span:
                                      "strides": None}
 
 
+def _create_and_exchange(nbytes, rank, world, group):
+  """cudaMalloc's an IPC-shareable buffer on this rank, swaps handles, maps the peers'.  Returns (own, ptrs)."""
+  L = _capi.lib()
+  own = ctypes.c_void_p()
+  handle = ctypes.create_string_buffer(64)
+  _capi.check(L.qmm_peer_buffer_create(nbytes, ctypes.byref(own), handle))
+  handles = [None] * world
+  dist.all_gather_object(handles, bytes(handle.raw), group=group)
+  ptrs = []
+  for r, h in enumerate(handles):
+    if r == rank:
+      ptrs.append(own.value)
+    else:
+      p = ctypes.c_void_p()
+      _capi.check(L.qmm_peer_buffer_open(h, ctypes.byref(p)))
+      ptrs.append(p.value)
+  return own.value, ptrs
+
+
+class FusedRowParallelDecode:
+  """Exchange buffers for ``qmm_rowparallel_decode``: the K-sharded decode linear whose kernel also sums the
+  partial results of all ranks (M <= 8).  One instance serves one out_features ``N``; every rank must make the
+  same calls in the same order."""
+
+  def __init__(self, N, max_M=8, group=None):
+    assert dist.is_initialized()
+    self.group, self.N, self.max_M = group, int(N), int(max_M)
+    self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+    self.device = torch.device("cuda", torch.cuda.current_device())
+    nbytes = _capi.lib().qmm_rowparallel_buffer_bytes(self.max_M, self.N, self.world)
+    self._own, self._ptrs = _create_and_exchange(nbytes, self.rank, self.world, group)
+    self._arr = (ctypes.c_void_p * self.world)(*self._ptrs)
+    dist.barrier(group=group)
+
+  def fits(self, M, N):
+    return N == self.N and 1 <= M <= min(self.max_M, 8)
+
+  def __call__(self, x_local, w, scaler, block_size=-1, weight_is_packed=False, out_dtype=torch.float32):
+    K = x_local.shape[-1]
+    x2 = x_local.reshape(-1, K)
+    x2 = x2 if x2.is_contiguous() else x2.contiguous()
+    M = x2.shape[0]
+    assert self.fits(M, w.shape[0]), f"M={M}, N={w.shape[0]} do not fit this exchange buffer (N={self.N}, M<={self.max_M})"
+    s32 = scaler if scaler.dtype == torch.float32 else scaler.float()
+    out = torch.empty((M, self.N), dtype=out_dtype, device=self.device)
+    _capi.check(_capi.lib().qmm_rowparallel_decode(
+        4 if weight_is_packed else 8, x2.data_ptr(), _capi.dtype_code(x2.dtype), w.data_ptr(), s32.contiguous().data_ptr(),
+        out.data_ptr(), _capi.dtype_code(out_dtype), M, self.N, K, 0 if block_size == -1 else block_size, self._arr,
+        self.rank, self.world, self.max_M * self.N, _capi.stream_ptr(self.device)))
+    return out.reshape(x_local.shape[:-1] + (self.N,))
+
+  def close(self):
+    if self._own is None:
+      return
+    torch.cuda.synchronize(self.device)
+    dist.barrier(group=self.group)
+    L = _capi.lib()
+    for r, p in enumerate(self._ptrs):
+      if r != self.rank:
+        _capi.check(L.qmm_peer_buffer_close(p))
+    dist.barrier(group=self.group)
+    _capi.check(L.qmm_peer_buffer_destroy(self._own))
+    self._own = None
+
+
 class PeerAllReduce:
   """Peer-mapped partial-result buffers of one process group (one process per GPU, same box).
 

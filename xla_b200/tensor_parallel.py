@@ -91,9 +91,12 @@ class RowParallelQuantizedLinear(torch.nn.Module):
 
   def __init__(self, w, scaler, zero_point=None, in_features=None, block_size=-1, int4_weight=False,
                weight_is_packed=False, out_dtype=None, reduce_dtype=torch.float32, group=None, local_op=None,
-               peer_reduce=None):
+               peer_reduce=None, fused_decode=None):
     super().__init__()
     self.group = group
+    # a xla_b200.peer_reduce.FusedRowParallelDecode: decode batches (M <= 8, symmetric weights) run the kernel
+    # that also sums over the ranks
+    self.fused_decode = fused_decode
     # a xla_b200.peer_reduce.PeerAllReduce: results that fit its buffers are summed by the one-shot
     # peer-memory kernel instead of the process group's all-reduce
     self.peer_reduce = peer_reduce
@@ -118,7 +121,12 @@ class RowParallelQuantizedLinear(torch.nn.Module):
 
   def forward(self, x_local):
     _, world = _world(self.group)
-    pr = self.peer_reduce
+    pr, fd = self.peer_reduce, self.fused_decode
+    if fd is not None and world > 1 and self.zero_point is None and self.local_op is _default_local_op:
+      M = x_local.numel() // x_local.shape[-1]
+      if fd.fits(M, self.weight.shape[0]) and x_local.dtype in (torch.bfloat16, torch.float16):
+        return fd(x_local, self.weight, self.weight_scaler, self.block_size, self.weight_is_packed,
+                  self.out_dtype if self.out_dtype is not None else torch.float32)
     if pr is not None and world > 1 and self.local_op is _default_local_op:
       M = x_local.numel() // x_local.shape[-1]
       N = self.weight.shape[0]
