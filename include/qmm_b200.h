@@ -254,7 +254,7 @@ QMM_API int qmm_allreduce_oneshot(void* const* data_ptrs, void* const* flag_ptrs
 
 /*
  * Row-parallel (K-sharded) decode linear with the sum over ranks fused into the kernel: every CTA writes its
- * 16 x M partial sums into this rank's exchange buffer, flags the tile on every peer, waits (bounded, ~1 s, then the
+ * 16 x M partial sums into every rank's exchange buffer (peer stores), flags the tile on every peer, waits (bounded, ~1 s, then the
  * device error word is set) for the same tile of every peer and stores the sum of the `world` partials, added in
  * rank order in fp32 - all ranks end up with bit-identical results and no separate all-reduce runs.
  *   out[m,n] = sum_r sum_b scale_r[b,n] * (sum_{k in block b of rank r's K slice} x_r[m,k] * w_r[n,k])

@@ -54,6 +54,18 @@ def test_argument_errors_need_no_gpu():
   # workspace size: xq + scales + row sums, 256-byte granules
   assert L.qmm_workspace_size(_capi.OP_W8A8_PERCHANNEL, 2048, 4096, 4096) == 2048 * 4096 + 2 * 8192
   assert L.qmm_workspace_size(_capi.OP_W8A16_PERCHANNEL, 16, 4096, 4096) == 0
+  # fused gate/up: the interleaved weight has a multiple of 16 rows
+  assert L.qmm_gate_up_decode(4, 1, 1, 1, 1, 1, 1, 1, 24, 128, 0, None) == 1
+  assert b"multiple of 16" in L.qmm_last_error_string()
+  # exchange buffers of the fused row-parallel kernel: two slots of `world` regions, one flag word per rank and tile
+  world, max_m, n = 8, 8, 8192
+  want = 2 * world * max_m * n * 4 + (world * (n // 16) + 2) * 4
+  assert L.qmm_rowparallel_buffer_bytes(max_m, n, world) == (want + 255) // 256 * 256
+  assert L.qmm_rowparallel_buffer_bytes(0, n, world) == 0
+  # one-shot all-reduce: whole float4 vectors only, at most 8 ranks
+  ptrs = (ctypes.c_void_p * 2)(16, 32)
+  assert L.qmm_allreduce_oneshot(ptrs, ptrs, 0, 2, 1, 64, 0, 6, None) == 1
+  assert L.qmm_allreduce_oneshot(ptrs, ptrs, 0, 9, 1, 64, 0, 8, None) == 1
   with pytest.raises(AssertionError):
     _capi.check(1)
   with pytest.raises(NotImplementedError):

@@ -516,7 +516,7 @@ int qmm_allreduce_oneshot(void* const* data_ptrs, void* const* flag_ptrs, int ra
 
 size_t qmm_rowparallel_buffer_bytes(int64_t max_M, int64_t N, int world) {
   if (max_M < 1 || N < 1 || world < 1) return 0;
-  const size_t data = 2 * (size_t)max_M * (size_t)N * sizeof(float);
+  const size_t data = 2 * (size_t)world * (size_t)max_M * (size_t)N * sizeof(float);
   const size_t flags = ((size_t)world * (size_t)((N + 15) / 16) + 2) * sizeof(uint32_t);
   return (data + flags + 255) / 256 * 256;
 }

@@ -111,12 +111,14 @@ __device__ __forceinline__ uint32_t sub_bias(uint32_t p, float bias) {
 __device__ __forceinline__ float silu_mul(float gate, float up) { return gate / (1.f + expf(-gate)) * up; }
 __device__ __forceinline__ int64_t gate_up_column(int64_t n) { return ((n >> 4) << 3) + (n & 7); }
 
-// Row-parallel exchange fused into the decode kernel (AR = true): the CTA's 16 x M partial sums go to this rank's
-// peer-visible buffer, the CTA tells every peer that ITS tile is there (one flag word per rank and tile, holding
+// Row-parallel exchange fused into the decode kernel (AR = true): the CTA's 16 x M partial sums go to the
+// peer-visible buffers, the CTA tells every peer that ITS tile is there (one flag word per rank and tile, holding
 // the call number), waits - bounded - for the same tile from every peer and writes the sum of the G partials, added
 // in rank order.  Tiles are exchanged as they finish, so the waiting of one CTA overlaps the weight stream of the
-// others.  Buffer layout (per rank): two data slots of slot_floats fp32 (call e uses slot e & 1), then
-// world x tiles flag words, then the call counter and a ticket.  The call number is kept in device memory, so a
+// others.  The partial sums are PUSHED: a CTA stores its tile into every rank's buffer, so the final sum reads local
+// memory only and the exchange costs one NVLink crossing, not a round trip.  Buffer layout (per rank): two slots
+// (call e uses slot e & 1) of `world` regions of slot_floats fp32, region r written by rank r; then world x tiles
+// flag words, then the call counter and a ticket.  The call number is kept in device memory, so a
 // launch captured in a CUDA graph stays valid on replay; the previous call of the stream has completed before
 // this one signals (it waits on griddepcontrol.wait first), which is what makes two slots enough.
 constexpr int kArMaxRanks = 8;
@@ -127,7 +129,7 @@ struct ArParams {
   uint32_t tiles;                // CTAs of the launch = flag words per rank
 };
 __device__ __forceinline__ uint32_t* ar_flags(const ArParams& a, int owner) {
-  return reinterpret_cast<uint32_t*>(a.data[owner] + 2 * (size_t)a.slot_floats);
+  return reinterpret_cast<uint32_t*>(a.data[owner] + 2 * (size_t)a.world * a.slot_floats);
 }
 __device__ __forceinline__ void ar_st_release(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -364,7 +366,9 @@ __global__ void __launch_bounds__(WARPS * 32)
     if (threadIdx.x == 0) s_epoch = *reinterpret_cast<volatile uint32_t*>(ctr) + 1u;
     __syncthreads();
     const uint32_t epoch = s_epoch;
-    float* own = ar.data[ar.rank] + (size_t)(epoch & 1u) * ar.slot_floats;
+    // push: my partial goes into region [slot][my rank] of EVERY rank's buffer (plain stores, local or over
+    // NVLink); the sum later reads local memory only
+    const size_t region = ((size_t)(epoch & 1u) * ar.world + ar.rank) * ar.slot_floats;
     for (int idx = threadIdx.x; idx < ROWS * NT * 8; idx += WARPS * 32) {
       const int row = idx % ROWS, tok = idx / ROWS;
       const int64_t n = n0 + row;
@@ -373,10 +377,14 @@ __global__ void __launch_bounds__(WARPS * 32)
 #pragma unroll
         for (int wi = 0; wi < WARPS; ++wi) v += s_part[wi][row][tok];
         if (!blockwise) v *= __ldg(scale + n);
-        own[(int64_t)tok * N + n] = v;
+        const size_t o = region + (size_t)tok * N + n;
+#pragma unroll
+        for (int r = 0; r < kArMaxRanks; ++r)
+          if (r < ar.world) ar.data[r][o] = v;
       }
     }
-    __threadfence_system();
+    // the barrier orders the CTA's stores before the signalling threads; their release stores (system scope,
+    // cumulative) then publish them - one fence per signal instead of one per thread
     __syncthreads();
     if (threadIdx.x < ar.world)
       ar_st_release(ar_flags(ar, threadIdx.x) + (size_t)ar.rank * ar.tiles + blockIdx.x, epoch);
@@ -396,13 +404,14 @@ __global__ void __launch_bounds__(WARPS * 32)
     }
     __syncthreads();
     if (s_ok) {
+      const float* mine = ar.data[ar.rank] + (size_t)(epoch & 1u) * ar.world * ar.slot_floats;
       for (int idx = threadIdx.x; idx < ROWS * NT * 8; idx += WARPS * 32) {
         const int row = idx % ROWS, tok = idx / ROWS;
         const int64_t n = n0 + row;
         if (n < N && tok < M) {
           const int64_t o = (int64_t)tok * N + n;
           float v = 0.f;
-          for (int r = 0; r < ar.world; ++r) v += ar_ld_peer(ar.data[r] + (size_t)(epoch & 1u) * ar.slot_floats + o);
+          for (int r = 0; r < ar.world; ++r) v += ar_ld_peer(mine + (size_t)r * ar.slot_floats + o);
           store_from_f32(out, o, out_dt, v);
         }
       }
