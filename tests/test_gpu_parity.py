@@ -577,6 +577,22 @@ def test_w8a16_blockwise_k_minor(M, with_zp):
   assert qo.max_abs_rel(out, exact) < TOL_F32
 
 
+def test_module_per_channel_int4_is_packed_once():
+  """XlaQuantizedLinear(int4_weight=True), per channel: the int8 container is packed to half the bytes on first use."""
+  g = qc.gen(52)
+  N, K, M = 512, 1024, 4
+  x = qc.activations(g, M, K)
+  w = qc.int4_weight(g, N, K)
+  s = qc.per_channel_scale(g, N)
+  m = xla_b200.XlaQuantizedLinear(K, N, is_symmetric=True, int4_weight=True)
+  m.load_quantized_weight(cu(w), cu(s))
+  y = m(cu(x))
+  wp, is_packed = m._packed_weight()
+  assert is_packed and wp.shape == (N, K // 2) and wp.dtype == torch.uint8
+  assert qo.max_abs_rel(y, qo.quantized_matmul(x, w, s, dot_round=None)) < TOL_F32
+  assert torch.equal(xla_b200.unpack_int4(wp).cpu(), w)
+
+
 def test_module_int8_blockwise_uses_k_minor_copy():
   """XlaQuantizedLinear(block_size>0, int8): reference layout in, K-minor copy built once, same results as the op."""
   g = qc.gen(51)

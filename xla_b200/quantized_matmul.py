@@ -248,9 +248,9 @@ class XlaQuantizedLinear(torch.nn.Module):
   Buffers (and ``state_dict`` keys): ``weight`` int8, ``weight_scaler``, ``zero_point`` (only when
   not symmetric).  Blockwise weights use the reference layout [in/block, block, out].
 
-  ``prepack=True`` additionally keeps a kernel-native, K-minor copy of a blockwise weight (int4 packed
-  two per byte along K, int8 transposed to [out, in]; built on first use on the GPU); the copy is derived
-  state and is not saved.
+  ``prepack=True`` additionally keeps a kernel-native, K-minor copy of the weight where that helps (int4
+  packed two per byte along K, for blockwise and per-channel int4 weights; blockwise int8 transposed to
+  [out, in]; built on first use on the GPU); the copy is derived state and is not saved.
   """
 
   def __init__(self, input_dim, output_dim, is_symmetric: bool = False, block_size: int = -1,
@@ -293,19 +293,23 @@ class XlaQuantizedLinear(torch.nn.Module):
     self._packed = None
 
   def _packed_weight(self):
-    """Kernel-native (K-minor) copy of a blockwise weight: packed int4 [N,K/2] or int8 [N,K]."""
+    """Kernel-native (K-minor) copy of the weight: packed int4 [N,K/2] (blockwise or per-channel int4), or
+    int8 [N,K] for a blockwise int8 weight."""
     w = self.weight
     key = (w.data_ptr(), w._version, w.device)
     if self._packed is None or self._packed[0] != key:
       from . import packed
       if self.int4_weight and self.input_dim % 2 == 0:
-        self._packed = (key, packed.pack_int4(w, layout="sbn"), True)
+        self._packed = (key, packed.pack_int4(w, layout="sbn" if w.dim() == 3 else "nk"), True)
       else:
         self._packed = (key, w.reshape(self.input_dim, -1).t().contiguous(), False)  # [S,bs,N] -> [N,K]
     return self._packed[1], self._packed[2]
 
   def forward(self, x):
-    if self.prepack and self.block_size != -1 and self.weight.is_cuda and self.weight.dim() == 3:
+    blockwise = self.block_size != -1 and self.weight.dim() == 3
+    per_channel_int4 = (self.block_size == -1 and self.int4_weight and self.weight.dim() == 2 and
+                        self.input_dim % 2 == 0 and not self.quantize_activation)
+    if self.prepack and self.weight.is_cuda and (blockwise or per_channel_int4):
       from . import packed
       w, is_packed = self._packed_weight()
       return packed.quantized_matmul_packed(
