@@ -43,6 +43,20 @@ __device__ __forceinline__ void mma_16816(float* c, const uint32_t* a, uint32_t 
   }
 }
 
+// same MMA as mma_16816 but not volatile: the compiler may interleave independent accumulator chains
+template <typename XT>
+__device__ __forceinline__ void mma_16816_nv(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  if constexpr (std::is_same<XT, __half>::value) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  } else {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+}
+
 // Bias carried by the converted weights.  The conversion drops an offset-binary nibble (v + 8) or byte
 // (v + 128) under the exponent of a power of two and does NOT subtract it again; the kernel removes
 // bias * sum_k x[m,k] instead, which the tensor core computes for free from the same activation
@@ -183,14 +197,13 @@ __global__ void __launch_bounds__(WARPS * 32)
     srow[r] = scale + n;
   }
 
-  // activation row of token (8*i + g) at this lane's offset inside a step; columns beyond M stay zero
+  // activation row of token (8*i + g) at this lane's offset inside a step; the columns of tokens beyond M
+  // are computed from token 0 and never stored (an MMA column depends on its own B column only)
   const XT* xrow[NT];
-  bool tok_ok[NT];
 #pragma unroll
   for (int i = 0; i < NT; ++i) {
     const int tok = 8 * i + g;
-    tok_ok[i] = tok < M;
-    xrow[i] = x + (int64_t)(tok_ok[i] ? tok : 0) * K + t * VPL;
+    xrow[i] = x + (int64_t)(tok < M ? tok : 0) * K + t * VPL;
   }
 
   float total[RG][NT][4], part[RG][NT][4], xsum[NT][4];
@@ -214,8 +227,7 @@ __global__ void __launch_bounds__(WARPS * 32)
       const uint4* xp = reinterpret_cast<const uint4*>(xrow[i] + (int64_t)step * VPS);
 #pragma unroll
       for (int q = 0; q < XREGS / 4; ++q) {
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (tok_ok[i]) v = __ldg(xp + q);
+        const uint4 v = __ldg(xp + q);  // an absent token reads token 0: its column is computed, never stored
         dst[i][4 * q] = v.x;
         dst[i][4 * q + 1] = v.y;
         dst[i][4 * q + 2] = v.z;
@@ -289,15 +301,15 @@ __global__ void __launch_bounds__(WARPS * 32)
           const uint32_t a_hi[4] = {pa[2], pb[2], pa[3], pb[3]};
 #pragma unroll
           for (int i = 0; i < NT; ++i) {
-            mma_16816<XT>(part[r][i], a_lo, xr[i][4 * wi], xr[i][4 * wi + 1]);
-            mma_16816<XT>(part[r][i], a_hi, xr[i][4 * wi + 2], xr[i][4 * wi + 3]);
+            mma_16816_nv<XT>(part[r][i], a_lo, xr[i][4 * wi], xr[i][4 * wi + 1]);
+            mma_16816_nv<XT>(part[r][i], a_hi, xr[i][4 * wi + 2], xr[i][4 * wi + 3]);
           }
         }
         if constexpr (kHasBias) {
 #pragma unroll
           for (int i = 0; i < NT; ++i) {
-            mma_16816<XT>(xsum[i], ones, xr[i][4 * wi], xr[i][4 * wi + 1]);
-            mma_16816<XT>(xsum[i], ones, xr[i][4 * wi + 2], xr[i][4 * wi + 3]);
+            mma_16816_nv<XT>(xsum[i], ones, xr[i][4 * wi], xr[i][4 * wi + 1]);
+            mma_16816_nv<XT>(xsum[i], ones, xr[i][4 * wi + 2], xr[i][4 * wi + 3]);
           }
         }
       } else {
@@ -315,11 +327,11 @@ __global__ void __launch_bounds__(WARPS * 32)
           }
           const uint32_t a[4] = {pa[0], pb[0], pa[1], pb[1]};
 #pragma unroll
-          for (int i = 0; i < NT; ++i) mma_16816<XT>(part[r][i], a, xr[i][2 * wi], xr[i][2 * wi + 1]);
+          for (int i = 0; i < NT; ++i) mma_16816_nv<XT>(part[r][i], a, xr[i][2 * wi], xr[i][2 * wi + 1]);
         }
         if constexpr (kHasBias) {
 #pragma unroll
-          for (int i = 0; i < NT; ++i) mma_16816<XT>(xsum[i], ones, xr[i][2 * wi], xr[i][2 * wi + 1]);
+          for (int i = 0; i < NT; ++i) mma_16816_nv<XT>(xsum[i], ones, xr[i][2 * wi], xr[i][2 * wi + 1]);
         }
       }
     }
@@ -467,17 +479,17 @@ __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int s
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
 
-// same MMA as mma_16816 but not volatile: the compiler may interleave independent accumulator chains
+// first MMA of an accumulator chain: C = 0 comes from the zero register, no accumulator set-up
 template <typename XT>
-__device__ __forceinline__ void mma_16816_nv(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+__device__ __forceinline__ void mma_16816_nv_first(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
   if constexpr (std::is_same<XT, __half>::value) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
   } else {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
   }
 }
 
@@ -486,7 +498,7 @@ struct StagedStep {  // one K step of a warp in flight: 16 bytes of two weight r
   float sc[2];
 };
 
-template <int WBITS, typename XT, int NT>
+template <int WBITS, typename XT, int NT, bool FOLD_EVERY>
 __global__ void __launch_bounds__(kStagedWarps * 32, 1)
     decode_mma_staged_kernel(const XT* __restrict__ x, const uint8_t* __restrict__ w, const float* __restrict__ scale,
                              void* __restrict__ out, int out_dt, int M, int N, int K, int steps_per_block,
@@ -501,6 +513,7 @@ __global__ void __launch_bounds__(kStagedWarps * 32, 1)
   constexpr int THREADS = kStagedWarps * 32;
   constexpr float kBias = Bias<XT, WBITS>::value;
   constexpr int kRedPitch = 17;
+  constexpr bool kLateFetch = NT == 4;
   static_assert(kStagedWarps * kRedPitch * ROWS_X * 4 <= 2 * STAGE_BYTES, "the reduction buffer reuses the ring");
   extern __shared__ __align__(16) unsigned char smem[];
 
@@ -510,26 +523,39 @@ __global__ void __launch_bounds__(kStagedWarps * 32, 1)
   const int64_t pitch = (int64_t)K * WBITS / 8;
   const int steps = K / VPS;
   const int nchunks = (steps + kChunkSteps - 1) / kChunkSteps;
-  // a step of this warp ends a scale block when the warp's next step lies in another block; with a
-  // stride of WK steps that is every step once WK is a multiple of the block length
-  const bool fold_every = blockwise && (WK % steps_per_block == 0);
-  // fragment reads: byte offset of this lane's first unit inside a step, and the swizzle it sees (the
-  // swizzle bit of unit 16*cs + 4*t + q, or 8*cs + 2*t + q, does not depend on q or on the step pair)
-  const int lane_unit = t * UPL;
+  // FOLD_EVERY: every step of this warp ends a scale block (blockwise, and the warp's stride of WK steps is
+  // a multiple of the block length); the per-step accumulators then start from zero in every step.
+  // Fragment reads: a lane reads UPL units of 16 bytes per token and step.  The swizzle bit of unit
+  // 16*ls + 4*t + q (int4) is bit 1 of t, a per-lane constant, and it only exchanges the unit pairs {0,1} and
+  // {2,3}; for int8 (unit 8*ls + 2*t + q) it is the parity of the step and moves the pair by +-2 units.
+  const uint32_t lane_row = (uint32_t)g * PITCH;
+  uint32_t off_a, off_b;  // int4: byte offsets of weight words {0,1} and {2,3}; int8: even / odd steps
+  if constexpr (WBITS == 4) {
+    const uint32_t sw = (uint32_t)(t >> 1) << 5;
+    off_a = lane_row + 64u * t + sw;
+    off_b = lane_row + 64u * t + (sw ^ 32u);
+  } else {
+    off_a = lane_row + 32u * t;
+    off_b = lane_row + ((32u * t) ^ 32u);
+  }
+  const int last_step = steps - 1;
 
   // cp.async of chunk c into ring slot c & 1 (tokens beyond M are zero-filled)
   const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
+  constexpr int ROW_STEP = THREADS / CHUNK_UNITS;  // token rows covered by one pass of the CTA
+  static_assert(THREADS % CHUNK_UNITS == 0, "a thread keeps its unit over the passes");
+  const int cp_u = tid % CHUNK_UNITS, cp_r = tid / CHUNK_UNITS;
+  const uint32_t cp_dst = smem_base + cp_r * PITCH + swz_unit(cp_u) * 16;
+  const XT* cp_src = x + (int64_t)cp_r * K + cp_u * 8;
   auto issue_chunk = [&](int c) {
     const int units_here = min(kChunkSteps, steps - c * kChunkSteps) * UPS;
-    const uint32_t dst0 = smem_base + (uint32_t)(c & 1) * STAGE_BYTES;
-    const XT* src0 = x + (int64_t)c * (kChunkSteps * VPS);
+    if (cp_u < units_here) {
+      const uint32_t dst = cp_dst + (uint32_t)(c & 1) * STAGE_BYTES;
+      const XT* src = cp_src + (int64_t)c * (kChunkSteps * VPS);
 #pragma unroll
-    for (int it = 0; it < ROWS_X * CHUNK_UNITS / THREADS; ++it) {
-      const int idx = tid + it * THREADS;
-      const int row = idx / CHUNK_UNITS, u = idx - row * CHUNK_UNITS;
-      if (u < units_here) {
-        const bool ok = row < M;
-        cp_async_16(dst0 + row * PITCH + swz_unit(u) * 16, src0 + (int64_t)(ok ? row : 0) * K + u * 8, ok ? 16 : 0);
+      for (int it = 0; it < ROWS_X / ROW_STEP; ++it) {
+        const bool ok = cp_r + it * ROW_STEP < M;
+        cp_async_16(dst + it * ROW_STEP * PITCH, ok ? (const void*)(src + (int64_t)it * ROW_STEP * K) : (const void*)x, ok ? 16 : 0);
       }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
@@ -549,8 +575,9 @@ __global__ void __launch_bounds__(kStagedWarps * 32, 1)
       wrow[r] = w + n * pitch + 16 * t;
       srow[r] = scale + n;
     }
+    // the step after which this warp adds its per-step sums, times the block scale, to the totals
     auto folds = [&](int s) {
-      if (fold_every) return true;
+      if constexpr (FOLD_EVERY) return true;
       const int sn = s + WK;
       if (sn >= steps) return true;
       if (!blockwise) return false;
@@ -558,12 +585,37 @@ __global__ void __launch_bounds__(kStagedWarps * 32, 1)
       const int bn = spb_shift >= 0 ? (sn >> spb_shift) : (sn / steps_per_block);
       return bn != b;
     };
+    // Weight and scale loads of the warp's steps, in step order.  In the four-tile FOLD_EVERY kernel the pointers
+    // just advance by the warp's stride; otherwise the address comes from the step index.  A step beyond the
+    // warp's share re-reads the last one (in bounds, never used).
+    const uint8_t* wp0 = wrow[0] + wk * 64;
+    const uint8_t* wp1 = wrow[1] + wk * 64;
+    const int64_t wstride = (int64_t)WK * 64;
+    const float *sp0 = srow[0], *sp1 = srow[1];
+    int64_t sstride = 0;
+    if constexpr (FOLD_EVERY && kLateFetch) {
+      sp0 += (int64_t)(wk >> spb_shift) * N;
+      sp1 += (int64_t)(wk >> spb_shift) * N;
+      sstride = (int64_t)(WK >> spb_shift) * N;
+    }
     auto fetch = [&](int s, StagedStep& d) {
-      if (active && s < steps) {
+      if constexpr (FOLD_EVERY && kLateFetch) {
+        d.w[0] = ld_stream_u4(wp0);
+        d.w[1] = ld_stream_u4(wp1);
+        d.sc[0] = __ldg(sp0);
+        d.sc[1] = __ldg(sp1);
+        if (s + WK < steps) {
+          wp0 += wstride;
+          wp1 += wstride;
+          sp0 += sstride;
+          sp1 += sstride;
+        }
+      } else {
+        const int sf = min(s, last_step);
 #pragma unroll
-        for (int r = 0; r < 2; ++r) d.w[r] = ld_stream_u4(wrow[r] + s * 64);
-        if (blockwise && folds(s)) {
-          const int b = spb_shift >= 0 ? (s >> spb_shift) : (s / steps_per_block);
+        for (int r = 0; r < 2; ++r) d.w[r] = ld_stream_u4(wrow[r] + sf * 64);
+        if (blockwise) {
+          const int b = spb_shift >= 0 ? (sf >> spb_shift) : (sf / steps_per_block);
 #pragma unroll
           for (int r = 0; r < 2; ++r) d.sc[r] = __ldg(srow[r] + (int64_t)b * N);
         }
@@ -575,8 +627,10 @@ __global__ void __launch_bounds__(kStagedWarps * 32, 1)
       qa.w[r] = qb.w[r] = make_uint4(0, 0, 0, 0);
       qa.sc[r] = qb.sc[r] = 1.f;
     }
-    fetch(wk, qa);
-    fetch(wk + WK, qb);
+    if (active && wk < steps) {
+      fetch(wk, qa);
+      fetch(wk + WK, qb);
+    }
     if (first) {
       // weights are static: their first loads may overlap the previous kernel of the stream; the
       // activations and every store of this kernel come after the wait
@@ -597,11 +651,18 @@ __global__ void __launch_bounds__(kStagedWarps * 32, 1)
     auto do_step = [&](int s, int c, StagedStep& q) {
       const uint4 w0 = q.w[0], w1 = q.w[1];
       const float sc0 = q.sc[0], sc1 = q.sc[1];
-      fetch(s + 2 * WK, q);
-      const int u0 = (s - c * kChunkSteps) * UPS + lane_unit;
-      const unsigned char* xb = smem + (c & 1) * STAGE_BYTES + g * PITCH;
+      if constexpr (!kLateFetch) fetch(s + 2 * WK, q);
+      const int ls = s - c * kChunkSteps;
+      const unsigned char* xs = smem + ((uint32_t)(c & 1) * STAGE_BYTES + (uint32_t)ls * (UPS * 16));
+      if constexpr (FOLD_EVERY && !kLateFetch) {
+#pragma unroll
+        for (int i = 0; i < NT; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) part[i][j] = 0.f;
+      }
       if constexpr (WBITS == 4) {
-        const int sw = ((u0 >> 3) & 1) << 1;
+        const unsigned char* xa = xs + off_a;
+        const unsigned char* xb = xs + off_b;
 #pragma unroll
         for (int wi = 0; wi < 4; ++wi) {
           uint32_t pa[4], pb[4];
@@ -614,17 +675,22 @@ __global__ void __launch_bounds__(kStagedWarps * 32, 1)
           }
           const uint32_t a_lo[4] = {pa[0], pb[0], pa[1], pb[1]};
           const uint32_t a_hi[4] = {pa[2], pb[2], pa[3], pb[3]};
-          const unsigned char* xp = xb + ((u0 + wi) ^ sw) * 16;
+          const unsigned char* xp = (wi < 2 ? xa : xb) + (wi & 1) * 16;
           uint4 xv[NT];
 #pragma unroll
           for (int i = 0; i < NT; ++i) xv[i] = *reinterpret_cast<const uint4*>(xp + i * 8 * PITCH);
 #pragma unroll
-          for (int i = 0; i < NT; ++i) mma_16816_nv<XT>(part[i], a_lo, xv[i].x, xv[i].y);
+          for (int i = 0; i < NT; ++i) {
+            if (FOLD_EVERY && kLateFetch && wi == 0)
+              mma_16816_nv_first<XT>(part[i], a_lo, xv[i].x, xv[i].y);
+            else
+              mma_16816_nv<XT>(part[i], a_lo, xv[i].x, xv[i].y);
+          }
 #pragma unroll
           for (int i = 0; i < NT; ++i) mma_16816_nv<XT>(part[i], a_hi, xv[i].z, xv[i].w);
         }
       } else {
-        const int sw = ((u0 >> 3) & 1) << 1;
+        const unsigned char* xq = xs + ((ls & 1) ? off_b : off_a);
 #pragma unroll
         for (int wp = 0; wp < 2; ++wp) {  // two weight words share one 16-byte activation unit
           uint32_t a[2][4];
@@ -645,16 +711,24 @@ __global__ void __launch_bounds__(kStagedWarps * 32, 1)
             a[h][2] = pa[1];
             a[h][3] = pb[1];
           }
-          const unsigned char* xp = xb + ((u0 + wp) ^ sw) * 16;
+          const unsigned char* xp = xq + wp * 16;
           uint4 xv[NT];
 #pragma unroll
           for (int i = 0; i < NT; ++i) xv[i] = *reinterpret_cast<const uint4*>(xp + i * 8 * PITCH);
 #pragma unroll
-          for (int i = 0; i < NT; ++i) mma_16816_nv<XT>(part[i], a[0], xv[i].x, xv[i].y);
+          for (int i = 0; i < NT; ++i) {
+            if (FOLD_EVERY && kLateFetch && wp == 0)
+              mma_16816_nv_first<XT>(part[i], a[0], xv[i].x, xv[i].y);
+            else
+              mma_16816_nv<XT>(part[i], a[0], xv[i].x, xv[i].y);
+          }
 #pragma unroll
           for (int i = 0; i < NT; ++i) mma_16816_nv<XT>(part[i], a[1], xv[i].z, xv[i].w);
         }
       }
+      // refill q for the step after next.  With four token tiles a step is long enough for the loads to land
+      // when they are issued at its end, which saves the register copies of q; with two tiles they go first.
+      if constexpr (kLateFetch) fetch(s + 2 * WK, q);
       if (folds(s)) {
 #pragma unroll
         for (int i = 0; i < NT; ++i) {
@@ -662,8 +736,10 @@ __global__ void __launch_bounds__(kStagedWarps * 32, 1)
           total[i][1] = fmaf(sc0, part[i][1], total[i][1]);
           total[i][2] = fmaf(sc1, part[i][2], total[i][2]);
           total[i][3] = fmaf(sc1, part[i][3], total[i][3]);
+          if constexpr (!FOLD_EVERY) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) part[i][j] = 0.f;
+            for (int j = 0; j < 4; ++j) part[i][j] = 0.f;
+          }
         }
       }
     };
@@ -754,18 +830,6 @@ cudaError_t launch_staged(const XT* xp, const uint8_t* wp, const float* scale, v
   constexpr int VPS = 512 / WBITS;
   constexpr int PITCH = kChunkSteps * (VPS * 2 / 16) * 16 + 16;
   constexpr size_t kSmem = 2 * (size_t)(NT * 8) * PITCH;
-  auto kern = decode_mma_staged_kernel<WBITS, XT, NT>;
-  static bool configured[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem);
-    if (e != cudaSuccess) return e;
-    configured[dev] = true;
-  } else if (dev >= 64) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem);
-    if (e != cudaSuccess) return e;
-  }
   const int tiles = (int)ceil_div(N, 16);
   const int grid = (int)std::min<int64_t>(sm_count(), tiles);
   const int per_cta = (int)ceil_div(tiles, grid);
@@ -773,6 +837,16 @@ cudaError_t launch_staged(const XT* xp, const uint8_t* wp, const float* scale, v
   while (tr < per_cta && tr < 8) tr *= 2;          // row tiles a CTA works on at a time
   const int wk = std::min(kStagedWarps / tr, 8);   // warps sharing the K steps of one tile
   const int rounds = (int)ceil_div(per_cta, tr);
+  const bool fold_every = bw && wk % spb == 0;
+  auto kern = fold_every ? decode_mma_staged_kernel<WBITS, XT, NT, true> : decode_mma_staged_kernel<WBITS, XT, NT, false>;
+  static bool configured[64][2] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 64 || !configured[dev][fold_every]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem);
+    if (e != cudaSuccess) return e;
+    if (dev < 64) configured[dev][fold_every] = true;
+  }
   return launch_pdl(kern, (unsigned)grid, kStagedWarps * 32, kSmem, st, xp, wp, scale, out, out_dt, (int)M, (int)N, (int)K, spb,
                     shift, bw, tiles, tr, wk, rounds, gate_up);
 }
