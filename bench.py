@@ -11,8 +11,9 @@ a different copy of the weights (a pool larger than L2), so no launch finds its 
              (steps are CUDA-graph replays, so launch latency of the Python layer is not in it).
   roofline   the dominant kernel's algorithmic bytes per launch / its average launch duration (CUDA
              events around each M's group of launches inside the timed region) vs the measured HBM peak.
-  e2e        same metric through the public op with HOST buffers: pinned-host activations copied in
-             and the result copied out inside the timed region, every step.
+  e2e        same metric through the public host-buffer API (xla_b200.HostPipeline: one library call per
+             linear does copy-in, kernel and copy-out): pinned-host activations in, result in pinned host
+             memory out, inside the timed region, every call; wall clock and CUDA events, the larger counts.
   cpu_baseline  the reference's CPU path (oracle/torch_port.py, same ATen operators) on the host
              cores, on a bounded sample.
 
@@ -533,52 +534,28 @@ def run_ours(args, rank, world, local_rank):
     barrier()
     total_ms = t_start.elapsed_time(t_end)
 
-    # ---- end to end through the public op: host buffers in, host result out, every step ----
+    # ---- end to end through the public host-buffer API: host activations in, host result out, every call ----
+    # xla_b200.HostPipeline does the copy-in, the linear and the copy-out of a call with ONE call into the
+    # library, on three streams of its own (the copies of neighbouring calls overlap the kernel).  The weights
+    # rotate through the same pool as in the device-resident timing.
+    import xla_b200
     hx = {m: torch.randn(m, wl.K).bfloat16().pin_memory() for m in wl.MS}
-    hy = {m: torch.empty(m, wl.N, dtype=torch.bfloat16).pin_memory() for m in wl.MS}
     e2e_reps = max(1, min(reps, 8))
-    # Host copies run on two side streams so that the copy-in of call i+1 and the copy-out of call i-1
-    # overlap the kernel of call i; hand-offs are events.  The copies and events are issued through the
-    # CUDA runtime bindings with an explicit stream (switching torch's current stream per call costs more
-    # host time than the kernel takes); the operator itself is called exactly as a user calls it.
-    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
-    xin = {m: [torch.empty(m, wl.K, dtype=torch.bfloat16, device=dev) for _ in range(e2e_reps)] for m in wl.MS}
-    try:
-      from cuda.bindings import runtime as rt
-      ev_in = [rt.cudaEventCreateWithFlags(rt.cudaEventDisableTiming)[1] for _ in range(e2e_reps)]
-      ev_k = [rt.cudaEventCreateWithFlags(rt.cudaEventDisableTiming)[1] for _ in range(e2e_reps)]
-      H2D, D2H = rt.cudaMemcpyKind.cudaMemcpyHostToDevice, rt.cudaMemcpyKind.cudaMemcpyDeviceToHost
-    except Exception as exc:  # bindings absent: plain in-order copies on the compute stream
-      print(f"[bench] CUDA runtime bindings unavailable ({exc}); end-to-end copies stay on the compute stream",
-            file=sys.stderr)
-      rt = None
-    h_in, h_c, h_out = s_in.cuda_stream, stream.cuda_stream, s_out.cuda_stream
+    hy = {m: [torch.empty(m, wl.N, dtype=torch.bfloat16).pin_memory() for _ in range(e2e_reps)] for m in wl.MS}
+    pipe = xla_b200.HostPipeline(max_M=max(wl.MS), K=wl.K, N=wl.N, depth=8, device=dev)
+    host_lin = [pipe.linear(wl.wp[i], wl.scale[i], block_size=wl.BS, weight_is_packed=True, variant=wl.forced)
+                for i in range(wl.copies)]
+    e2e_i = [0]
 
     def e2e_step():
-      keep = []
+      i = e2e_i[0]
       for m in wl.MS:
-        if rt is None:
-          for _ in range(e2e_reps):
-            xd = hx[m].to(dev, non_blocking=True)
-            y = wl.launch(m, xd)
-            hy[m].copy_(y, non_blocking=True)
-          continue
-        nin, nout = 2 * m * wl.K, 2 * m * wl.N
-        src, dst = hx[m].data_ptr(), hy[m].data_ptr()
-        for i in range(e2e_reps):
-          xd = xin[m][i]  # one staging buffer per call of the step: no reuse before the final synchronize
-          rt.cudaMemcpyAsync(xd.data_ptr(), src, nin, H2D, h_in)
-          rt.cudaEventRecord(ev_in[i], h_in)
-          rt.cudaStreamWaitEvent(h_c, ev_in[i], 0)
-          y = wl.launch(m, xd)
-          rt.cudaEventRecord(ev_k[i], h_c)
-          rt.cudaStreamWaitEvent(h_out, ev_k[i], 0)
-          rt.cudaMemcpyAsync(dst, y.data_ptr(), nout, D2H, h_out)
-          keep.append(y)  # alive until the copy-out stream has been synchronised
-        # the next batch size reuses the events: its copies are ordered behind these on the same streams
-      s_in.synchronize()
-      stream.synchronize()
-      s_out.synchronize()
+        x_host, outs = hx[m], hy[m]
+        for r in range(e2e_reps):
+          i = i + 1 if i + 1 < wl.copies else 0
+          host_lin[i](x_host, outs[r])
+      e2e_i[0] = i
+      pipe.synchronize()  # every result of the step is in its host buffer
 
     for _ in range(max(3, args.warmup)):
       e2e_step()
@@ -591,6 +568,13 @@ def run_ours(args, rank, world, local_rank):
     e1.record(stream)
     barrier()
     e2e_ms = max(e0.elapsed_time(e1), 1e3 * (time.perf_counter() - w0))
+    # the last host result of the last step against the device operator on the same inputs
+    m_last, i_last = wl.MS[-1], e2e_i[0]
+    ref = wl.op(hx[m_last].to(dev), wl.wp[i_last], wl.scale[i_last], block_size=wl.BS, int4_weight=True,
+                weight_is_packed=True, out_dtype=torch.bfloat16)
+    if not torch.equal(ref.cpu(), hy[m_last][e2e_reps - 1]):
+      raise RuntimeError("end-to-end result differs from the device operator")
+    pipe.close()
   clocks = sampler.stop() if rank == 0 else None
   extras = {}
   if not args.headline_only:

@@ -274,6 +274,38 @@ QMM_API int qmm_rowparallel_decode(int wbits, const void* x, int x_dtype, const 
                            void* const* peer_bufs, int rank, int world, int64_t slot_floats, void* stream);
 
 /*
+ * Host-buffer front end of the weight-only linears: one call copies the activations in from HOST memory, runs
+ * the linear and copies the result out to HOST memory, on three streams of the pipeline's own that overlap the
+ * copies of neighbouring calls with the kernel.  The reference has no such call: a user of the reference moves
+ * the activation to the XLA device (`x.to(xla_device)`, torch_xla/csrc/tensor_util.cpp), runs
+ * torch.ops.xla.quantized_matmul on it (torch_xla/experimental/xla_quantized_matmul.py:79-114, :133-170) and
+ * reads the result back (`y.cpu()`); this entry is that round trip as one enqueue.
+ *
+ *   qmm_host_pipeline_create   allocates, on the current device, `depth` (1..64) staging slots of max_x_bytes +
+ *                              max_out_bytes and the streams and events; nothing is allocated afterwards.
+ *   qmm_host_weight_only       enqueues one linear.  x_host [M,K] and out_host [M,N] are HOST pointers (page-locked
+ *                              for the copies to overlap); w, scale, zp are DEVICE pointers in the layout `layout`
+ *                              names, with the meaning they have in the device entry point of that layout.  Returns
+ *                              once the work is enqueued; when more than `depth` calls are in flight it first waits
+ *                              for the oldest.  out_host is valid after qmm_host_pipeline_sync.
+ *   qmm_host_pipeline_sync     blocks until every result submitted so far is in its host buffer.
+ *   qmm_host_pipeline_destroy  waits for the pipeline's streams and frees everything.
+ * A pipeline is used by one host thread at a time, on the device it was created on.
+ */
+typedef enum qmm_host_layout {
+  QMM_HOST_W4_BLOCKWISE_PACKED = 0,  /* as qmm_w4a16_blockwise_packed */
+  QMM_HOST_W4_PERCHANNEL_PACKED = 1, /* as qmm_w4a16_perchannel_packed (block_size ignored) */
+  QMM_HOST_W8_PERCHANNEL = 2,        /* as qmm_w8a16_perchannel (block_size ignored) */
+  QMM_HOST_W8_BLOCKWISE_KMINOR = 3,  /* as qmm_w8a16_blockwise */
+} qmm_host_layout;
+QMM_API int qmm_host_pipeline_create(size_t max_x_bytes, size_t max_out_bytes, int depth, void** pipeline);
+QMM_API int qmm_host_weight_only(void* pipeline, int layout, const void* x_host, int x_dtype, const void* w,
+                                 const float* scale, const float* zp, void* out_host, int out_dtype, int64_t M,
+                                 int64_t N, int64_t K, int64_t block_size, int variant);
+QMM_API int qmm_host_pipeline_sync(void* pipeline);
+QMM_API int qmm_host_pipeline_destroy(void* pipeline);
+
+/*
  * Device-side error word of the current device.  Kernels that wait on hardware barriers give up
  * after a bounded number of polls and record a non-zero code here instead of hanging.
  * Reads the word back (this call synchronises `stream`), stores it in *flag (HOST pointer) and

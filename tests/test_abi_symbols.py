@@ -66,6 +66,14 @@ def test_argument_errors_need_no_gpu():
   ptrs = (ctypes.c_void_p * 2)(16, 32)
   assert L.qmm_allreduce_oneshot(ptrs, ptrs, 0, 2, 1, 64, 0, 6, None) == 1
   assert L.qmm_allreduce_oneshot(ptrs, ptrs, 0, 9, 1, 64, 0, 8, None) == 1
+  # host pipeline: argument checks come before any CUDA call
+  handle = ctypes.c_void_p()
+  assert L.qmm_host_pipeline_create(0, 16, 2, ctypes.byref(handle)) == 1
+  assert L.qmm_host_pipeline_create(16, 16, 65, ctypes.byref(handle)) == 1
+  assert L.qmm_host_pipeline_create(16, 16, 2, None) == 6
+  assert L.qmm_host_weight_only(None, 0, 16, 1, 16, 16, None, 16, 1, 1, 4, 128, 128, 0) == 6
+  assert L.qmm_host_pipeline_sync(None) == 6
+  assert L.qmm_host_pipeline_destroy(None) == 0
   with pytest.raises(AssertionError):
     _capi.check(1)
   with pytest.raises(NotImplementedError):

@@ -730,3 +730,36 @@ def test_torch_compile_and_cuda_graph_pass_through():
     gr.replay()
     st.synchronize()
   assert torch.equal(y, eager)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("packed,block_size", [(True, 128), (True, -1), (False, 128), (False, -1)])
+def test_host_pipeline_matches_the_device_op(packed, block_size):
+  """Host buffers in, host buffers out through one library call per linear: bit-identical to the device
+  operator on the same inputs, for more calls than the pipeline has staging slots and for varying M."""
+  import xla_b200
+  dev = torch.device("cuda:0")
+  g = torch.Generator().manual_seed(11)
+  N, K = 1024, 512
+  w = torch.randint(-8 if packed else -128, 8 if packed else 128, (N, K), generator=g, dtype=torch.int8)
+  sshape = (N,) if block_size == -1 else (K // block_size, N)
+  scale = (torch.rand(sshape, generator=g) * 0.04 + 0.01).to(dev)
+  wd = w.to(dev)
+  if packed:
+    wd = xla_b200.pack_int4(wd)
+  pipe = xla_b200.HostPipeline(max_M=32, K=K, N=N, depth=3, device=dev)
+  lin = pipe.linear(wd, scale, block_size=block_size, weight_is_packed=packed)
+  calls = []
+  for i, M in enumerate([1, 8, 32, 5, 16, 32, 1, 9]):
+    xh = torch.randn(M, K, generator=g).bfloat16().pin_memory()
+    yh = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+    lin(xh, yh)
+    calls.append((xh, yh))
+  pipe.synchronize()
+  for xh, yh in calls:
+    ref = torch.ops.xla_b200.quantized_matmul_packed(xh.to(dev), wd, scale, block_size=block_size, int4_weight=packed,
+                                                     weight_is_packed=packed, out_dtype=torch.bfloat16)
+    assert torch.equal(ref.cpu(), yh)
+  with pytest.raises(Exception):
+    lin(torch.zeros(64, K, dtype=torch.bfloat16).pin_memory(), torch.empty(64, N, dtype=torch.bfloat16).pin_memory())
+  pipe.close()

@@ -13,9 +13,10 @@ from . import packed  # noqa: F401
 from .packed import pack_int4, quantized_matmul_packed, unpack_int4  # noqa: F401
 from . import mlp  # noqa: F401
 from .mlp import concat_projections, interleave_gate_up, quantized_gate_up, split_outputs  # noqa: F401
+from .host import HostLinear, HostPipeline  # noqa: F401
 
 __all__ = [
     "XlaQuantizedLinear", "force_variant", "quantize_tensor", "set_activation_saturation", "pack_int4",
     "unpack_int4", "quantized_matmul_packed", "interleave_gate_up", "quantized_gate_up", "concat_projections",
-    "split_outputs"
+    "split_outputs", "HostPipeline", "HostLinear"
 ]

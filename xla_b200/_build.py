@@ -9,7 +9,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libqmm_b200.so")
 SOURCES = ["abi.cu", "generic.cu", "gemv.cu", "act_quant.cu", "pack.cu", "w8a8_gemm.cu", "mixed_gemm.cu", "decode_mma.cu", "decode_tc.cu",
-           "static_scratch.cu", "peer_reduce.cu"]
+           "static_scratch.cu", "peer_reduce.cu", "host_pipeline.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math=false",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-cudart", "static",

@@ -29,6 +29,10 @@ SIGNATURES = {
     "qmm_w8a16_perchannel": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i, _p]),
     "qmm_w4a16_perchannel_packed": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i, _p]),
     "qmm_w8a16_blockwise": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _p]),
+    "qmm_host_pipeline_create": (_i, [_sz, _sz, _i, ctypes.POINTER(ctypes.c_void_p)]),
+    "qmm_host_weight_only": (_i, [_p, _i, _p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i]),
+    "qmm_host_pipeline_sync": (_i, [_p]),
+    "qmm_host_pipeline_destroy": (_i, [_p]),
     "qmm_peer_buffer_create": (_i, [_sz, ctypes.POINTER(ctypes.c_void_p), ctypes.c_char_p]),
     "qmm_peer_buffer_open": (_i, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]),
     "qmm_peer_buffer_close": (_i, [_p]),
