@@ -54,7 +54,7 @@ def outlier_activations(gen, m, k, dtype):
 
 def main():
   ap = argparse.ArgumentParser()
-  ap.add_argument("--reference", default="/root/reference")
+  ap.add_argument("--reference", required=True, help="checkout of the reference project (pytorch/xla)")
   ap.add_argument("--out", default=os.path.join(os.path.dirname(os.path.abspath(__file__)),
                                                  "qmm_golden.npz"))
   args = ap.parse_args()
