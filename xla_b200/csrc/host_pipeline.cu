@@ -100,7 +100,6 @@ extern "C" int qmm_host_weight_only(void* pipeline, int layout, const void* x_ho
                                     const float* scale, const float* zp, void* out_host, int out_dtype, int64_t M,
                                     int64_t N, int64_t K, int64_t block_size, int variant) {
   if (!pipeline) return qmm::fail(QMM_ERR_NULL, "host_weight_only: null pipeline");
-  if (!x_host || !out_host) return qmm::fail(QMM_ERR_NULL, "host_weight_only: null host buffer");
   if (M < 0 || N < 0 || K < 0) return qmm::fail(QMM_ERR_BAD_SHAPE, "negative dimension");
   if (x_dtype != QMM_F32 && x_dtype != QMM_BF16 && x_dtype != QMM_F16) return qmm::fail(QMM_ERR_UNSUPPORTED, "host_weight_only: x dtype %d", x_dtype);
   if (out_dtype != QMM_F32 && out_dtype != QMM_BF16 && out_dtype != QMM_F16)
@@ -110,7 +109,8 @@ extern "C" int qmm_host_weight_only(void* pipeline, int layout, const void* x_ho
   if (xb > p->x_bytes || ob > p->out_bytes)
     return qmm::fail(QMM_ERR_WORKSPACE, "host_weight_only: the call needs %zu + %zu staging bytes, the pipeline has %zu + %zu", xb, ob,
                      p->x_bytes, p->out_bytes);
-  if (M * N == 0) return QMM_OK;
+  if (M * N == 0) return QMM_OK;  // an empty call is a no-op, as in the device entry points
+  if (!x_host || !out_host) return qmm::fail(QMM_ERR_NULL, "host_weight_only: null host buffer");
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev != p->device)
     return qmm::fail(QMM_ERR_DEVICE, "host_weight_only: the pipeline belongs to device %d, current device is %d", p->device, dev);
