@@ -6,7 +6,7 @@
 //
 //   out[m,n] = sum_b scale[b,n] * (sum_{k in block b} x[m,k] * w[n,k])       (per-channel: one block)
 //
-// Mapping.  A CTA of 4 warps owns 16 consecutive output rows n; warp w takes the K steps s = w, w+4, ...
+// Mapping.  A CTA of W warps (4, 8 or 16: see launch_nt) owns 16 consecutive output rows n; warp w takes the K steps s = w, w+W, ...
 // One step covers 64 bytes of each weight row (128 int4 or 64 int8 values): lane (g = lane/4,
 // t = lane%4) loads 16 bytes of row g and of row g+8 at byte offset 16*t of the step, i.e. each lane
 // owns a contiguous k span and the four lanes of a quad own the whole step.  Because the contraction
@@ -876,8 +876,26 @@ int launch_nt(const void* x, const void* w, const float* scale, void* out, int o
     a.tiles = (uint32_t)ceil_div(N, 16);
     err = launch_pdl(decode_mma_kernel<WBITS, XT, 1, 1, 4, true>, (unsigned)ceil_div(N, 16), 128, 0, st, xp, wp, scale, out,
                      out_dt, (int)M, N, K, spb, shift, bw, 0, a, device_error_word());
-  } else if (M <= 8)
-    err = QMM_DECODE_LAUNCH(1, 1, 4);
+  } else if (M <= 8) {
+    // Warps per 16-row tile.  With few row tiles (a narrow projection, a tensor-parallel shard) four warps per
+    // tile leave an SM with a dozen warps, too few to cover the load latency; more warps then share the tile's K
+    // steps.  Thresholds measured on B200 (M = 1 and 8): int4 weights 16 warps up to 512 tiles (8192 x 28672:
+    // 76.7 -> 46.4 us; 4096 x 4096: 9.2 -> 5.2 us) and 4 from 896 tiles on; int8 weights 16 warps up to 256 tiles
+    // (4096 x 4096: 12.9 -> 5.7 us), 8 up to 896 tiles (14336 x 4096: 20.6 -> 16.6 us; 8192 x 8192: 37.9 -> 16.9 us),
+    // 4 at 1792 tiles.
+    const int64_t tiles = ceil_div(N, 16), sms = sm_count();
+    int warps;
+    if (WBITS == 4)
+      warps = tiles < 5 * sms ? 16 : 4;
+    else
+      warps = tiles < 2 * sms ? 16 : tiles < 8 * sms ? 8 : 4;
+    if (warps >= 16)
+      err = QMM_DECODE_LAUNCH(1, 1, 16);
+    else if (warps >= 8)
+      err = QMM_DECODE_LAUNCH(1, 1, 8);
+    else
+      err = QMM_DECODE_LAUNCH(1, 1, 4);
+  }
   else if (M <= 16)
     err = launch_staged<WBITS, XT, 2>(xp, wp, scale, out, out_dt, M, N, K, spb, shift, bw, gate_up, st);
   else
