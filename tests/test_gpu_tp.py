@@ -79,7 +79,9 @@ def _worker(rank, world, port, results):
         for _ in range(3):
           y_f = row_f(h_local)
           ok &= y_f.shape == y.shape and y_f.dtype == y.dtype
-          ok &= torch.equal(y_f, y_p)  # same partials, same order of addition, same rounding
+          # same order of addition over the ranks; inside a tile the two paths may split K over a different number
+          # of warps (the exchange kernel always uses four), so the partial sums agree to fp32 rounding only
+          ok &= qo.max_abs_rel(y_f, y_p) < 1e-2 and qo.max_abs_rel(y_f, y_full) < 1e-2
         gathered = [torch.empty_like(y_f) for _ in range(world)]
         dist.all_gather(gathered, y_f)
         ok &= all(torch.equal(t, gathered[0]) for t in gathered)

@@ -869,26 +869,30 @@ int launch_nt(const void* x, const void* w, const float* scale, void* out, int o
              scale, out, out_dt, (int)M, N, K, spb, shift, bw, gate_up, ArParams{}, (uint32_t*)nullptr)
   // one token tile: many small CTAs, activations through L1 (64 KB for 8 tokens of 4096);
   // two or four tiles: one CTA per SM with the activations staged in shared memory
+  //
+  // Warps per 16-row tile of the one-token-tile kernel.  With few row tiles (a narrow projection, a tensor-parallel
+  // shard) four warps per tile leave an SM with a dozen warps, too few to cover the load latency; more warps then
+  // share the tile's K steps.  Thresholds measured on B200 (M = 1 and 8): int4 weights 16 warps up to 512 tiles
+  // (8192 x 28672: 76.7 -> 46.4 us; 4096 x 4096: 9.2 -> 5.2 us) and 4 from 896 tiles on; int8 weights 16 warps up to
+  // 256 tiles (4096 x 4096: 12.9 -> 5.7 us), 8 up to 896 tiles (14336 x 4096: 20.6 -> 16.6 us; 8192 x 8192:
+  // 37.9 -> 16.9 us), 4 at 1792 tiles.
+  const int64_t tiles = ceil_div(N, 16), sms = sm_count();
+  int warps;
+  if (WBITS == 4)
+    warps = tiles < 5 * sms ? 16 : 4;
+  else
+    warps = tiles < 2 * sms ? 16 : tiles < 8 * sms ? 8 : 4;
   cudaError_t err;
   if (ar) {
     if (M > 8 || gate_up) return fail(QMM_ERR_UNSUPPORTED, "fused row-parallel exchange: M <= 8 only (got %lld)", (long long)M);
     ArParams a = *ar;
-    a.tiles = (uint32_t)ceil_div(N, 16);
-    err = launch_pdl(decode_mma_kernel<WBITS, XT, 1, 1, 4, true>, (unsigned)ceil_div(N, 16), 128, 0, st, xp, wp, scale, out,
-                     out_dt, (int)M, N, K, spb, shift, bw, 0, a, device_error_word());
+    a.tiles = (uint32_t)tiles;
+    // always four warps per tile here: a CTA that waits for its peers' tiles holds its SM slot, and with 16-warp
+    // CTAs only one is resident per SM, so nothing else would run under the wait (measured: 86 vs 81 us on the
+    // two-GPU MLP)
+    err = launch_pdl(decode_mma_kernel<WBITS, XT, 1, 1, 4, true>, (unsigned)tiles, 128, 0, st, xp, wp, scale, out, out_dt,
+                     (int)M, N, K, spb, shift, bw, 0, a, device_error_word());
   } else if (M <= 8) {
-    // Warps per 16-row tile.  With few row tiles (a narrow projection, a tensor-parallel shard) four warps per
-    // tile leave an SM with a dozen warps, too few to cover the load latency; more warps then share the tile's K
-    // steps.  Thresholds measured on B200 (M = 1 and 8): int4 weights 16 warps up to 512 tiles (8192 x 28672:
-    // 76.7 -> 46.4 us; 4096 x 4096: 9.2 -> 5.2 us) and 4 from 896 tiles on; int8 weights 16 warps up to 256 tiles
-    // (4096 x 4096: 12.9 -> 5.7 us), 8 up to 896 tiles (14336 x 4096: 20.6 -> 16.6 us; 8192 x 8192: 37.9 -> 16.9 us),
-    // 4 at 1792 tiles.
-    const int64_t tiles = ceil_div(N, 16), sms = sm_count();
-    int warps;
-    if (WBITS == 4)
-      warps = tiles < 5 * sms ? 16 : 4;
-    else
-      warps = tiles < 2 * sms ? 16 : tiles < 8 * sms ? 8 : 4;
     if (warps >= 16)
       err = QMM_DECODE_LAUNCH(1, 1, 16);
     else if (warps >= 8)
