@@ -61,6 +61,8 @@ typedef enum qmm_variant {
   QMM_VARIANT_TCGEN05 = 3, /* TMA -> shared memory -> tcgen05.mma with TMEM accumulators */
   QMM_VARIANT_MMA = 4,     /* decode: weights dequantised in registers into warp-level MMAs, M <= 32 */
   QMM_VARIANT_TMEM = 5,    /* decode: weights dequantised in registers into tensor memory, tcgen05.mma, M <= 32 */
+  QMM_VARIANT_I8TC = 6,    /* activations split into int8 limbs, unconverted weights into tcgen05.mma.kind::i8, stream-K
+                              over all SMs, 1 <= M <= 64; only through qmm_weight_only (needs workspace) */
 } qmm_variant;
 
 typedef enum qmm_op {
@@ -93,6 +95,10 @@ QMM_API int qmm_w8a16_perchannel(const void* x, int x_dtype, const int8_t* w, co
  * Replaces: torch.ops.xla.quantized_matmul with block_size > 0
  *   (xla_quantized_matmul.py:115-124 and :160-170; layout check :27-53).
  * w: int8 [S,bs,N]; scale, zp: f32 [S,N]; zp may be NULL.
+ * Only QMM_VARIANT_AUTO / QMM_VARIANT_GENERIC: this N-minor layout runs on the any-shape kernel (one thread per
+ * output).  It is the correctness path; for speed convert the weight once to a K-minor layout (qmm_pack_int4_sbn,
+ * or a transposed int8 copy) and call qmm_weight_only - what the operator layer above this ABI does on its own,
+ * caching the converted weight per weight tensor.
  */
 QMM_API int qmm_blockwise_sbn(const void* x, int x_dtype, const int8_t* w, const float* scale,
                       const float* zp, void* out, int out_dtype, int64_t M, int64_t N, int64_t K,
@@ -129,6 +135,26 @@ QMM_API int qmm_w4a16_perchannel_packed(const void* x, int x_dtype, const uint8_
 QMM_API int qmm_w8a16_blockwise(const void* x, int x_dtype, const int8_t* w, const float* scale, const float* zp,
                         void* out, int out_dtype, int64_t M, int64_t N, int64_t K, int64_t block_size, int variant,
                         void* stream);
+
+/*
+ * Any of the four weight-only linears above on K-minor weights, with caller scratch: the one entry point that can
+ * run QMM_VARIANT_I8TC, which QMM_VARIANT_AUTO prefers for 1 <= M <= 64 when it applies and the workspace suffices
+ * (otherwise AUTO chooses as the entry points above do, and the workspace is not touched).
+ *   wbits 8: w int8 [N,K];  wbits 4: w uint8 [N,K/2], nibble order as qmm_w4a16_blockwise_packed.
+ *   block_size <= 0: per-channel, scale/zp f32 [N];  block_size > 0: scale/zp f32 [K/block_size, N].
+ *   workspace: qmm_weight_only_workspace_size(max M, K) bytes of device memory, 256-byte aligned, whose first
+ *   1024 bytes are ZERO before the first call (the kernel leaves them zero); calls that share a workspace must be
+ *   ordered on the GPU (same stream).  NULL / 0 is allowed and rules the I8TC variant out.
+ * I8TC computes  sum_k X[m,k] * w[n,k]  exactly in int32, where X is the activation row in 22-bit fixed point
+ * relative to the row's largest exponent (exact for bf16/f16 values within 2^-14 of the row maximum, rounded at
+ * 2^-22 of it below), then applies scales in fp32: the accuracy of an fp32 accumulation.
+ * Replaces: torch.ops.xla.quantized_matmul without activation quantization
+ *   (torch_xla/experimental/xla_quantized_matmul.py:101-124 XLA key, :152-170 CPU key).
+ */
+QMM_API size_t qmm_weight_only_workspace_size(int64_t max_M, int64_t K);
+QMM_API int qmm_weight_only(int wbits, const void* x, int x_dtype, const void* w, const float* scale, const float* zp,
+                    void* out, int out_dtype, int64_t M, int64_t N, int64_t K, int64_t block_size, int variant,
+                    void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * Fused gate + up projection of a gated MLP for decode batches (1 <= M <= 32, bf16/f16 activations):
@@ -288,9 +314,13 @@ QMM_API int qmm_rowparallel_decode(int wbits, const void* x, int x_dtype, const 
  *                              names, with the meaning they have in the device entry point of that layout.  Returns
  *                              once the work is enqueued; when more than `depth` calls are in flight it first waits
  *                              for the oldest.  out_host is valid after qmm_host_pipeline_sync.
+ *   qmm_host_pipeline_wait_stream  makes every linear submitted from now on wait for the work that `stream` holds at
+ *                              this moment: call it after preparing weights or scales on another stream (packing,
+ *                              an upload) - the pipeline's own streams are not ordered after the caller's otherwise.
  *   qmm_host_pipeline_sync     blocks until every result submitted so far is in its host buffer.
  *   qmm_host_pipeline_destroy  waits for the pipeline's streams and frees everything.
- * A pipeline is used by one host thread at a time, on the device it was created on.
+ * A pipeline is used by one host thread at a time, on the device it was created on.  x_host must stay untouched
+ * until the call's copy-in has run (at the latest: qmm_host_pipeline_sync).
  */
 typedef enum qmm_host_layout {
   QMM_HOST_W4_BLOCKWISE_PACKED = 0,  /* as qmm_w4a16_blockwise_packed */
@@ -302,6 +332,7 @@ QMM_API int qmm_host_pipeline_create(size_t max_x_bytes, size_t max_out_bytes, i
 QMM_API int qmm_host_weight_only(void* pipeline, int layout, const void* x_host, int x_dtype, const void* w,
                                  const float* scale, const float* zp, void* out_host, int out_dtype, int64_t M,
                                  int64_t N, int64_t K, int64_t block_size, int variant);
+QMM_API int qmm_host_pipeline_wait_stream(void* pipeline, void* stream);
 QMM_API int qmm_host_pipeline_sync(void* pipeline);
 QMM_API int qmm_host_pipeline_destroy(void* pipeline);
 
@@ -312,6 +343,16 @@ QMM_API int qmm_host_pipeline_destroy(void* pipeline);
  * clears it.  Returns QMM_ERR_TIMEOUT if it was non-zero.
  */
 QMM_API int qmm_device_error_flag(uint32_t* flag, void* stream);
+
+/*
+ * How long the kernels that wait for another GPU (qmm_allreduce_oneshot, qmm_rowparallel_decode) keep waiting
+ * before they give up: `seconds` of SM clock at about 2 GHz, in (0, 60]; the default is about one second.  On
+ * expiry the kernel sets the device error word (code 7: all-reduce kernel, 8: fused decode exchange; the peer's
+ * rank in bits 8 and up), fills its result with NaN and returns; the context stays usable.  Process-wide; applies
+ * to launches made after the call.  Stands in for the reference's collective timeouts, which live in the PJRT
+ * runtime (torch_xla/csrc/runtime/), not in this operator.
+ */
+QMM_API int qmm_set_peer_wait_limit(double seconds);
 
 /*
  * Pipeline tracing for the tensor-core weight-only kernel: while a device buffer of 4 x 1024 int64 is

@@ -1,0 +1,127 @@
+"""GPU parity of the split-activation tensor-core kernel (variant "i8tc": unconverted int8/int4 weights into
+tcgen05.mma.kind::i8, stream-K over all SMs) against the CPU oracle, through the operators and the C ABI.
+
+The kernel's integer sums are exact and its fixed-point activations are exact for values within 2^-14 of the row
+maximum, so fp32 outputs are held to 1e-4 (max|a-b| / max|b|) against the exact value of the formula and 16-bit
+outputs to 1e-2, the tolerances of the other weight-only kernels.
+"""
+import pytest
+import torch
+
+import xla_b200
+from oracle import qmm_oracle as qo
+from tests import qmm_cases as qc
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+TOL_BF16 = 1e-2
+TOL_F32 = 1e-4
+
+
+def packed_op(*args, variant="i8tc", **kw):
+  with xla_b200.force_variant(variant):
+    return torch.ops.xla_b200.quantized_matmul_packed(*args, **kw)
+
+
+def _exact(x, w_nk, s, bs):
+  if bs > 0:
+    return qo.quantized_matmul(x.float(), qc.to_sbn(w_nk, bs), s, block_size=bs, dot_round=None)
+  return qo.quantized_matmul(x.float(), w_nk, s, dot_round=None)
+
+
+def _run(x, w_nk, s, bs, wbits, out_dtype):
+  wd = w_nk.to(DEV)
+  if wbits == 4:
+    wd = xla_b200.pack_int4(wd)
+  return packed_op(x.to(DEV), wd, s.to(DEV), block_size=bs if bs > 0 else -1, int4_weight=wbits == 4,
+                   weight_is_packed=wbits == 4, out_dtype=out_dtype)
+
+
+# every token-count class of the kernel (limb columns 16, 32, 48, 96, 192) and both edges of each
+@pytest.mark.parametrize("M", [1, 2, 5, 6, 10, 11, 16, 17, 32, 33, 64])
+@pytest.mark.parametrize("wbits,bs", [(8, 0), (8, 128), (4, 128), (4, 0)])
+def test_token_classes(M, wbits, bs):
+  g = qc.gen(100 + M)
+  N, K = 1536, 2048
+  x = qc.activations(g, M, K)
+  w = qc.int4_weight(g, N, K) if wbits == 4 else qc.int8_weight(g, N, K)
+  s = qc.blockwise_scale(g, K // bs, N) if bs > 0 else qc.per_channel_scale(g, N)
+  exact = _exact(x, w, s, bs)
+  out = _run(x, w, s, bs, wbits, torch.float32)
+  assert out.dtype == torch.float32 and tuple(out.shape) == (M, N)
+  assert qo.max_abs_rel(out, exact) < TOL_F32
+  out16 = _run(x, w, s, bs, wbits, torch.bfloat16)
+  assert qo.max_abs_rel(out16, exact) < TOL_BF16
+
+
+# ragged N (last tile partly empty), K tails (not a multiple of the 128-value stage), few tiles with a long K
+# (every tile is shared by many CTAs), many tiles with a short K
+@pytest.mark.parametrize("N,K,wbits,bs", [
+    (1000, 4096, 8, 0), (1000, 4096 + 16, 8, 0), (130, 8192, 8, 0), (3001, 256, 8, 128), (256, 28672, 4, 128),
+    (1000, 4096 + 32, 4, 0), (1111, 4096 + 96, 4, 0), (8192, 128, 8, 128), (77, 1024, 4, 256), (512, 3072, 8, 512),
+    (640, 2304, 4, 128),
+])
+@pytest.mark.parametrize("M", [3, 24])
+def test_ragged_shapes(N, K, wbits, bs, M):
+  g = qc.gen(N + K + M)
+  x = qc.activations(g, M, K)
+  w = qc.int4_weight(g, N, K) if wbits == 4 else qc.int8_weight(g, N, K)
+  s = qc.blockwise_scale(g, K // bs, N) if bs > 0 else qc.per_channel_scale(g, N)
+  out = _run(x, w, s, bs, wbits, torch.float32)
+  assert qo.max_abs_rel(out, _exact(x, w, s, bs)) < TOL_F32
+
+
+@pytest.mark.parametrize("xdt", [torch.float32, torch.float16, torch.bfloat16])
+def test_activation_dtypes_and_ranges(xdt):
+  g = qc.gen(7)
+  M, N, K = 8, 512, 1024
+  x = qc.activations(g, M, K, dtype=torch.float32, outliers=True)
+  x[1] *= 1e-3   # rows of very different magnitude: the exponent is per row
+  x[2] *= 250.0
+  x[3] = 0.0     # an all-zero row
+  x[4, ::2] = 0.0
+  x = x.to(xdt)
+  w = qc.int8_weight(g, N, K)
+  s = qc.per_channel_scale(g, N)
+  exact = _exact(x, w, s, 0)
+  out = _run(x, w, s, 0, 8, torch.float32).cpu()
+  assert torch.all(out[3] == 0)
+  for m in range(M):
+    if m != 3:
+      assert qo.max_abs_rel(out[m], exact[m]) < TOL_F32, m
+
+
+def test_largest_int8_products_do_not_overflow():
+  # every limb of row 0 at -128 (top limb -63) against weights of -127 over the longest supported accumulation
+  M, N, K = 2, 128, 65536
+  X = -(63 * 65536 + 128 * 256 + 128)
+  x = torch.full((M, K), X * 2.0 ** -21, dtype=torch.float32)  # exact in fp32, exponent 0
+  x[1, ::2] = 255.0 / 256.0
+  w = torch.full((N, K), -127, dtype=torch.int8)
+  w[:, 1::2] = 127
+  w[0] = -127
+  s = torch.ones(N)
+  out = _run(x, w, s, 0, 8, torch.float32)
+  assert qo.max_abs_rel(out, _exact(x, w, s, 0)) < 1e-6
+
+
+def test_deterministic_and_workspace_left_clean():
+  g = qc.gen(11)
+  M, N, K = 16, 384, 8192   # three tiles over all SMs: every tile is summed from many partial tiles
+  x, w, s = qc.activations(g, M, K), qc.int8_weight(g, N, K), qc.per_channel_scale(g, N)
+  outs = [_run(x, w, s, 0, 8, torch.float32) for _ in range(10)]
+  for o in outs[1:]:
+    assert torch.equal(o, outs[0])
+  assert qo.max_abs_rel(outs[0], _exact(x, w, s, 0)) < TOL_F32
+
+
+def test_auto_picks_it_and_reference_op_reaches_it():
+  from xla_b200 import _capi
+  g = qc.gen(3)
+  M, N, K = 16, 4096, 4096   # the W8A16 per-channel configuration
+  x, w, s = qc.activations(g, M, K), qc.int8_weight(g, N, K), qc.per_channel_scale(g, N)
+  out = torch.ops.xla.quantized_matmul(x.to(DEV), w.to(DEV), s.to(DEV))
+  assert out.dtype == torch.float32
+  assert qo.max_abs_rel(out, _exact(x, w, s, 0)) < TOL_F32
+  assert _capi.lib().qmm_weight_only_workspace_size(16, 4096) > 0

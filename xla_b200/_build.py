@@ -8,7 +8,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libqmm_b200.so")
-SOURCES = ["abi.cu", "generic.cu", "gemv.cu", "act_quant.cu", "pack.cu", "w8a8_gemm.cu", "mixed_gemm.cu", "decode_mma.cu", "decode_tc.cu",
+SOURCES = ["abi.cu", "generic.cu", "gemv.cu", "act_quant.cu", "pack.cu", "w8a8_gemm.cu", "mixed_gemm.cu", "limb_gemm.cu", "decode_mma.cu", "decode_tc.cu",
            "static_scratch.cu", "peer_reduce.cu", "host_pipeline.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math=false",
@@ -44,7 +44,7 @@ def build(force=False, verbose=False):
     o = os.path.join(obj_dir, src.replace(".cu", ".o"))
     objs.append(o)
     if force or _stale(o, [s] + headers):
-      cmd = [nvcc] + [f for f in NVCC_FLAGS if f != "--use_fast_math=false"] + ["-c", s, "-o", o]
+      cmd = [nvcc] + [f for f in NVCC_FLAGS if f != "--use_fast_math=false"] + os.environ.get("QMM_NVCC_EXTRA", "").split() + ["-c", s, "-o", o]
       if verbose:
         cmd.insert(1, "-Xptxas=-v")
       procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))

@@ -11,10 +11,10 @@ import torch
 from . import _build
 
 F32, BF16, F16 = 0, 1, 2
-AUTO, GENERIC, GEMV, TCGEN05, MMA, TMEM = 0, 1, 2, 3, 4, 5
+AUTO, GENERIC, GEMV, TCGEN05, MMA, TMEM, I8TC = 0, 1, 2, 3, 4, 5, 6
 OP_W8A16_PERCHANNEL, OP_BLOCKWISE_SBN, OP_W4A16_BLOCKWISE_PACKED, OP_W8A8_PERCHANNEL, OP_W4A16_PERCHANNEL_PACKED = range(5)
 
-VARIANTS = {"auto": AUTO, "generic": GENERIC, "gemv": GEMV, "tcgen05": TCGEN05, "mma": MMA, "tmem": TMEM}
+VARIANTS = {"auto": AUTO, "generic": GENERIC, "gemv": GEMV, "tcgen05": TCGEN05, "mma": MMA, "tmem": TMEM, "i8tc": I8TC}
 
 _DTYPES = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
 
@@ -29,8 +29,11 @@ SIGNATURES = {
     "qmm_w8a16_perchannel": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i, _p]),
     "qmm_w4a16_perchannel_packed": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i, _p]),
     "qmm_w8a16_blockwise": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _p]),
+    "qmm_weight_only_workspace_size": (_sz, [_i64, _i64]),
+    "qmm_weight_only": (_i, [_i, _p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _p, _sz, _p]),
     "qmm_host_pipeline_create": (_i, [_sz, _sz, _i, ctypes.POINTER(ctypes.c_void_p)]),
     "qmm_host_weight_only": (_i, [_p, _i, _p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i]),
+    "qmm_host_pipeline_wait_stream": (_i, [_p, _p]),
     "qmm_host_pipeline_sync": (_i, [_p]),
     "qmm_host_pipeline_destroy": (_i, [_p]),
     "qmm_peer_buffer_create": (_i, [_sz, ctypes.POINTER(ctypes.c_void_p), ctypes.c_char_p]),
@@ -54,6 +57,7 @@ SIGNATURES = {
     "qmm_pack_int4_sbn": (_i, [_p, _p, _i64, _i64, _i64, _p]),
     "qmm_unpack_int4_nk": (_i, [_p, _p, _i64, _i64, _p]),
     "qmm_device_error_flag": (_i, [_p, _p]),
+    "qmm_set_peer_wait_limit": (_i, [ctypes.c_double]),
     "qmm_debug_set_trace": (_i, [_p]),
     "qmm_variant_for": (ctypes.c_char_p, [_i, _i64, _i64, _i64, _i64, _i]),
 }
@@ -118,6 +122,28 @@ def on_device(device, fn):
     return fn()
 
 
+_workspaces = {}
+
+
+def workspace(device, max_M, K):
+  """Scratch for ``qmm_weight_only`` on torch's current stream of `device`: (pointer, bytes), or (None, 0) when no
+  variant needs one.  One buffer per (device, stream), zero-filled when created (the kernels keep its flag words
+  zero) and grown on demand; a stream capture in progress never allocates - it gets the existing buffer or none."""
+  need = lib().qmm_weight_only_workspace_size(min(max_M, 64), K)
+  if need == 0:
+    return None, 0
+  idx = device.index if device.index is not None else torch.cuda.current_device()
+  key = (idx, stream_ptr(idx))
+  buf = _workspaces.get(key)
+  if buf is None or buf.numel() < need:
+    if torch.cuda.is_current_stream_capturing():
+      return (None, 0) if buf is None else (buf.data_ptr(), buf.numel())
+    size = max(need, 16 << 20) if buf is None else max(need, 2 * buf.numel())
+    buf = torch.zeros(size, dtype=torch.uint8, device=torch.device("cuda", idx))
+    _workspaces[key] = buf
+  return buf.data_ptr(), buf.numel()
+
+
 def check(status):
   """Turns a non-zero qmm_status into the Python exception the reference would raise."""
   if status == 0:
@@ -125,6 +151,27 @@ def check(status):
   L = lib()
   msg = L.qmm_last_error_string().decode() or L.qmm_status_string(status).decode()
   raise _STATUS_EXC.get(status, RuntimeError)(f"qmm_b200[{L.qmm_status_string(status).decode()}]: {msg}")
+
+
+def device_error(device=None):
+  """Reads and clears the device error word of `device` (synchronises torch's current stream there); returns the
+  raw word, 0 when healthy.  Bits 0-7: which bounded wait gave up, bits 8 and up: the CTA or the peer rank."""
+  dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+  word = ctypes.c_uint32(0)
+
+  def read():
+    lib().qmm_device_error_flag(ctypes.byref(word), stream_ptr(dev))
+
+  on_device(dev, read)
+  return word.value
+
+
+def check_device(device=None):
+  """Raises TimeoutError if a kernel on `device` gave up a bounded wait since the last check."""
+  word = device_error(device)
+  if word:
+    raise TimeoutError(f"qmm_b200: a device-side wait gave up (code {word & 0xff}, unit {word >> 8}); results of the "
+                       "affected call are NaN or undefined")
 
 
 def require_cuda(*tensors):

@@ -1,6 +1,7 @@
 // extern "C" entry points of libqmm_b200 (declared in include/qmm_b200.h): argument checks,
 // kernel-family selection, and the host-side helpers the kernels share.
 #include <cuda.h>
+#include <atomic>
 #include <stdarg.h>
 #include <stdio.h>
 #include <string.h>
@@ -80,6 +81,9 @@ uint32_t* device_error_word() {
   }
   return cached[dev];
 }
+
+static std::atomic<long long> g_peer_wait_cycles{2000000000ll};  // about a second of SM clock
+long long peer_wait_cycles() { return g_peer_wait_cycles.load(std::memory_order_relaxed); }
 
 static long long* g_trace = nullptr;
 long long* debug_trace_buffer() { return g_trace; }
@@ -229,18 +233,12 @@ int qmm_blockwise_sbn(const void* x, int x_dtype, const int8_t* w, const float* 
                 (long long)K, (long long)block_size);
   if (M * N == 0) return QMM_OK;
   cudaStream_t st = as_stream(stream);
-  if (variant == QMM_VARIANT_AUTO)
-    variant = gemv_sbn_supported(M, N, K, block_size, w) ? QMM_VARIANT_GEMV : QMM_VARIANT_GENERIC;
-  switch (variant) {
-    case QMM_VARIANT_GENERIC:
-      log_choice("blockwise_sbn", "generic", M, N, K);
-      return launch_generic_sbn(x, x_dtype, w, scale, zp, out, out_dtype, M, N, K, block_size, st);
-    case QMM_VARIANT_GEMV:
-      log_choice("blockwise_sbn", "gemv", M, N, K);
-      return launch_gemv_sbn(x, x_dtype, w, scale, zp, out, out_dtype, M, N, K, block_size, st);
-    default:
-      return fail(QMM_ERR_UNSUPPORTED, "blockwise_sbn: variant %d is not available for this layout", variant);
-  }
+  // This layout (N minor) is served by the any-shape kernel only: the streaming kernels want K-minor rows, and the
+  // callers above this entry convert a weight once (qmm_pack_int4_sbn, or a transposed copy) and keep it.
+  if (variant != QMM_VARIANT_AUTO && variant != QMM_VARIANT_GENERIC)
+    return fail(QMM_ERR_UNSUPPORTED, "blockwise_sbn: variant %d is not available for this layout", variant);
+  log_choice("blockwise_sbn", "generic", M, N, K);
+  return launch_generic_sbn(x, x_dtype, w, scale, zp, out, out_dtype, M, N, K, block_size, st);
 }
 
 int qmm_w4a16_blockwise_packed(const void* x, int x_dtype, const uint8_t* wp, const float* scale,
@@ -311,6 +309,43 @@ int qmm_w8a16_blockwise(const void* x, int x_dtype, const int8_t* w, const float
     default:
       return fail(QMM_ERR_UNSUPPORTED, "unknown variant %d", variant);
   }
+}
+
+size_t qmm_weight_only_workspace_size(int64_t max_M, int64_t K) {
+  if (max_M > 64) max_M = 64;  // larger batches never use the scratch
+  return limb_tc_workspace_bytes(max_M, K);
+}
+
+int qmm_weight_only(int wbits, const void* x, int x_dtype, const void* w, const float* scale, const float* zp, void* out,
+                    int out_dtype, int64_t M, int64_t N, int64_t K, int64_t block_size, int variant, void* workspace,
+                    size_t workspace_bytes, void* stream) {
+  if (wbits != 4 && wbits != 8) return fail(QMM_ERR_BAD_SHAPE, "weight_only: wbits must be 4 or 8, got %d", wbits);
+  if (block_size < 0) block_size = 0;
+  if (variant == QMM_VARIANT_AUTO || variant == QMM_VARIANT_I8TC) {
+    int rc = check_common(x, x_dtype, w, scale, out, out_dtype, M, N, K);
+    if (rc != QMM_OK || M * N == 0) return rc;
+    if (block_size > 0 && K % block_size != 0)
+      return fail(QMM_ERR_BAD_SHAPE, "input_dim should be divisible by block_size, got input_dim: %lld, block_size: %lld",
+                  (long long)K, (long long)block_size);
+    const bool can = limb_tc_supported(wbits, M, N, K, block_size, x, x_dtype, w, zp != nullptr) && workspace &&
+                     workspace_bytes >= limb_tc_workspace_bytes(M, K) && aligned(workspace, 256);
+    if (variant == QMM_VARIANT_I8TC || (can && limb_tc_preferred(wbits, M, N, K, block_size))) {
+      log_choice("weight_only", "i8tc", M, N, K);
+      if (zp) return fail(QMM_ERR_UNSUPPORTED, "the split-activation tensor-core kernel does not take a zero point");
+      return launch_limb_tc(wbits, x, x_dtype, w, scale, out, out_dtype, M, N, K, block_size, 0, workspace, workspace_bytes,
+                            as_stream(stream));
+    }
+  }
+  if (wbits == 8) {
+    if (block_size > 0)
+      return qmm_w8a16_blockwise(x, x_dtype, static_cast<const int8_t*>(w), scale, zp, out, out_dtype, M, N, K, block_size, variant,
+                                 stream);
+    return qmm_w8a16_perchannel(x, x_dtype, static_cast<const int8_t*>(w), scale, zp, out, out_dtype, M, N, K, variant, stream);
+  }
+  if (block_size > 0)
+    return qmm_w4a16_blockwise_packed(x, x_dtype, static_cast<const uint8_t*>(w), scale, zp, out, out_dtype, M, N, K, block_size,
+                                      variant, stream);
+  return qmm_w4a16_perchannel_packed(x, x_dtype, static_cast<const uint8_t*>(w), scale, zp, out, out_dtype, M, N, K, variant, stream);
 }
 
 int qmm_gate_up_decode(int wbits, const void* x, int x_dtype, const void* w, const float* scale, void* out,
@@ -553,6 +588,12 @@ int qmm_device_error_flag(uint32_t* flag, void* stream) {
   return QMM_OK;
 }
 
+int qmm_set_peer_wait_limit(double seconds) {
+  if (!(seconds > 0.0) || seconds > 60.0) return fail(QMM_ERR_BAD_SHAPE, "peer wait limit must be in (0, 60] seconds, got %g", seconds);
+  g_peer_wait_cycles.store((long long)(seconds * 2.0e9), std::memory_order_relaxed);  // ~2 GHz SM clock
+  return QMM_OK;
+}
+
 int qmm_debug_set_trace(void* device_buffer) {
   g_trace = reinterpret_cast<long long*>(device_buffer);
   return QMM_OK;
@@ -573,7 +614,7 @@ const char* qmm_variant_for(int op, int64_t M, int64_t N, int64_t K, int64_t blo
       return "generic";
     }
     case QMM_OP_BLOCKWISE_SBN:
-      return gemv_sbn_supported(M, N, K, block_size, ok) ? "gemv" : "generic";
+      return "generic";
     case QMM_OP_W8A8_PERCHANNEL:
       return (M >= 16 && K % 16 == 0 && K >= 16) ? "tcgen05" : "generic";
     default:

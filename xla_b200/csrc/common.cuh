@@ -19,6 +19,9 @@ inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s
 // Word that kernels with bounded waits set when a wait gives up (0 = healthy).
 uint32_t* device_error_word();  // device address of the flag for the current device, or nullptr
 
+// How long a kernel waits for another GPU before it gives up, in SM clock cycles (qmm_set_peer_wait_limit).
+long long peer_wait_cycles();
+
 // Caller-provided device buffer for pipeline timestamps (nullptr = tracing off).
 long long* debug_trace_buffer();
 

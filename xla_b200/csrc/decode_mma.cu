@@ -141,6 +141,7 @@ struct ArParams {
   int rank, world;
   uint32_t slot_floats;          // fp32 elements per data slot (>= M * N)
   uint32_t tiles;                // CTAs of the launch = flag words per rank
+  long long wait_cycles;         // how long a CTA waits for its peers' tiles before it gives up
 };
 __device__ __forceinline__ uint32_t* ar_flags(const ArParams& a, int owner) {
   return reinterpret_cast<uint32_t*>(a.data[owner] + 2 * (size_t)a.world * a.slot_floats);
@@ -168,6 +169,7 @@ __global__ void __launch_bounds__(WARPS * 32)
     decode_mma_kernel(const XT* __restrict__ x, const uint8_t* __restrict__ w, const float* __restrict__ scale,
                       void* __restrict__ out, int out_dt, int M, int64_t N, int64_t K, int steps_per_block,
                       int spb_shift, int blockwise, int gate_up, const ArParams ar, uint32_t* err_word) {
+  // ar.wait_cycles bounds the wait for the peers' tiles (AR only)
   constexpr int VPS = 512 / WBITS;      // values of one weight row per step: 128 (int4) or 64 (int8)
   constexpr int VPL = VPS / 4;          // values per lane per row per step: 32 or 16
   constexpr int XREGS = VPL / 2;        // packed activation pairs per lane per token tile: 16 or 8
@@ -407,7 +409,7 @@ __global__ void __launch_bounds__(WARPS * 32)
       const long long t0 = clock64();
       uint32_t spins = 0;
       while ((int32_t)(ar_ld_acquire(f) - epoch) < 0) {
-        if ((++spins & 0x3ff) == 0 && clock64() - t0 > 2000000000ll) {  // about a second: give up, report
+        if ((++spins & 0x3ff) == 0 && clock64() - t0 > ar.wait_cycles) {  // give up, report
           s_ok = 0;
           if (err_word) atomicCAS(err_word, 0u, 8u | ((uint32_t)threadIdx.x << 8));
           break;
@@ -426,6 +428,13 @@ __global__ void __launch_bounds__(WARPS * 32)
           for (int r = 0; r < ar.world; ++r) v += ar_ld_peer(mine + (size_t)r * ar.slot_floats + o);
           store_from_f32(out, o, out_dt, v);
         }
+      }
+    } else {
+      // a peer's tile never arrived (the device error word says which rank): NaN instead of stale memory
+      for (int idx = threadIdx.x; idx < ROWS * NT * 8; idx += WARPS * 32) {
+        const int row = idx % ROWS, tok = idx / ROWS;
+        const int64_t n = n0 + row;
+        if (n < N && tok < M) store_from_f32(out, (int64_t)tok * N + n, out_dt, __uint_as_float(0x7fc00000u));
       }
     }
     // the CTA that finishes last advances the call counter (every CTA has read it by then)
@@ -931,6 +940,7 @@ int launch_decode_mma_allreduce(int wbits, const void* x, int x_dt, const void* 
   a.rank = rank;
   a.world = world;
   a.slot_floats = (uint32_t)slot_floats;
+  a.wait_cycles = peer_wait_cycles();
   if (wbits == 4) {
     if (x_dt == QMM_BF16) return launch_nt<4, __nv_bfloat16>(x, w, scale, out, out_dt, M, N, K, block_size, 0, st, &a);
     return launch_nt<4, __half>(x, w, scale, out, out_dt, M, N, K, block_size, 0, st, &a);

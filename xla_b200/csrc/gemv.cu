@@ -290,11 +290,4 @@ int launch_gemv_nk(int wbits, const void* x, int x_dt, const void* w, const floa
   return QMM_OK;
 }
 
-bool gemv_sbn_supported(int64_t, int64_t, int64_t, int64_t, const void*) { return false; }
-
-int launch_gemv_sbn(const void*, int, const int8_t*, const float*, const float*, void*, int, int64_t,
-                    int64_t, int64_t, int64_t, cudaStream_t) {
-  return fail(QMM_ERR_UNSUPPORTED, "gemv on the [S,bs,N] layout is not built; use the generic kernel");
-}
-
 }  // namespace qmm

@@ -77,22 +77,23 @@ __global__ void generic_sbn_kernel(const void* __restrict__ x, int x_dt,
                                    const float* __restrict__ zp, void* __restrict__ out, int out_dt,
                                    int64_t M, int64_t N, int64_t K, int64_t block_size) {
   const int64_t n = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t m = blockIdx.y;
-  if (n >= N || m >= M) return;
+  if (n >= N) return;
   const int64_t S = K / block_size;
-  float total = 0.f;
-  for (int64_t b = 0; b < S; ++b) {
-    float part = 0.f, xs = 0.f;
-    for (int64_t c = 0; c < block_size; ++c) {
-      const int64_t k = b * block_size + c;
-      const float xv = load_as_f32(x, m * K + k, x_dt);
-      part = fmaf(xv, (float)w[k * N + n], part);
-      xs += xv;
+  for (int64_t m = blockIdx.y; m < M; m += gridDim.y) {  // the grid's y extent is capped: rows beyond it loop
+    float total = 0.f;
+    for (int64_t b = 0; b < S; ++b) {
+      float part = 0.f, xs = 0.f;
+      for (int64_t c = 0; c < block_size; ++c) {
+        const int64_t k = b * block_size + c;
+        const float xv = load_as_f32(x, m * K + k, x_dt);
+        part = fmaf(xv, (float)w[k * N + n], part);
+        xs += xv;
+      }
+      total = fmaf(scale[b * N + n], part, total);
+      if (zp) total = fmaf(-xs, zp[b * N + n], total);
     }
-    total = fmaf(scale[b * N + n], part, total);
-    if (zp) total = fmaf(-xs, zp[b * N + n], total);
+    store_from_f32(out, m * N + n, out_dt, total);
   }
-  store_from_f32(out, m * N + n, out_dt, total);
 }
 
 // int8 x int8 -> int32, exact, with the fp32 epilogue in the reference's operation order.
@@ -148,8 +149,7 @@ int launch_generic_nk(bool packed, const void* x, int x_dt, const void* w, const
 int launch_generic_sbn(const void* x, int x_dt, const int8_t* w, const float* scale, const float* zp,
                        void* out, int out_dt, int64_t M, int64_t N, int64_t K, int64_t block_size,
                        cudaStream_t st) {
-  if (M > 65535) return fail(QMM_ERR_UNSUPPORTED, "generic kernel: M=%lld too large", (long long)M);
-  dim3 grid((unsigned)ceil_div(N, 128), (unsigned)M);
+  dim3 grid((unsigned)ceil_div(N, 128), (unsigned)(M < 65535 ? M : 65535));
   generic_sbn_kernel<<<grid, 128, 0, st>>>(x, x_dt, w, scale, zp, out, out_dt, M, N, K, block_size);
   return check_launch("generic_sbn_kernel");
 }

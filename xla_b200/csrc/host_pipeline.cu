@@ -25,6 +25,9 @@ struct HostPipeline {
   cudaStream_t s_in = nullptr, s_k = nullptr, s_out = nullptr;
   std::vector<void*> xd, yd;
   std::vector<cudaEvent_t> ev_in, ev_k, ev_out;
+  cudaEvent_t ev_dep = nullptr;  // orders the kernel stream after work the caller enqueued elsewhere
+  void* ws = nullptr;            // scratch of the split-activation tensor-core kernel (zero-filled once)
+  size_t ws_bytes = 0;
   unsigned long long calls = 0;
 };
 
@@ -36,6 +39,8 @@ void release(HostPipeline* p) {
   for (auto* v : {&p->ev_in, &p->ev_k, &p->ev_out})
     for (cudaEvent_t e : *v)
       if (e) cudaEventDestroy(e);
+  if (p->ev_dep) cudaEventDestroy(p->ev_dep);
+  if (p->ws) cudaFree(p->ws);
   for (cudaStream_t s : {p->s_in, p->s_k, p->s_out})
     if (s) cudaStreamDestroy(s);
   delete p;
@@ -68,6 +73,14 @@ extern "C" int qmm_host_pipeline_create(size_t max_x_bytes, size_t max_out_bytes
     for (auto* v : {&p->ev_in, &p->ev_k, &p->ev_out})
       if (e == cudaSuccess) e = cudaEventCreateWithFlags(&(*v)[i], cudaEventDisableTiming);
   }
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&p->ev_dep, cudaEventDisableTiming);
+  if (e == cudaSuccess) {
+    // scratch for the kernels that want it: limbs of at most max_x_bytes / 2 activations (three bytes each), the
+    // per-CTA partial tiles and the flag words; one buffer serves every call because the kernel stream orders them
+    p->ws_bytes = 3 * (max_x_bytes / 2) + (size_t)qmm::kLimbMaxCtas * 64 * 128 * 4 + 8192;
+    e = cudaMalloc(&p->ws, p->ws_bytes);
+    if (e == cudaSuccess) e = cudaMemset(p->ws, 0, p->ws_bytes);
+  }
   if (e != cudaSuccess) {
     release(p);
     cudaGetLastError();
@@ -83,6 +96,18 @@ extern "C" int qmm_host_pipeline_sync(void* pipeline) {
   cudaError_t e = cudaStreamSynchronize(p->s_out);
   if (e == cudaSuccess) e = cudaStreamSynchronize(p->s_k);
   if (e != cudaSuccess) return qmm::fail(QMM_ERR_DEVICE, "host_pipeline_sync: %s", cudaGetErrorString(e));
+  return QMM_OK;
+}
+
+extern "C" int qmm_host_pipeline_wait_stream(void* pipeline, void* stream) {
+  if (!pipeline) return qmm::fail(QMM_ERR_NULL, "host_pipeline_wait_stream: null pipeline");
+  auto* p = static_cast<HostPipeline*>(pipeline);
+  cudaError_t e = cudaEventRecord(p->ev_dep, reinterpret_cast<cudaStream_t>(stream));
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(p->s_k, p->ev_dep, 0);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return qmm::fail(QMM_ERR_DEVICE, "host_pipeline_wait_stream: %s", cudaGetErrorString(e));
+  }
   return QMM_OK;
 }
 
@@ -125,27 +150,19 @@ extern "C" int qmm_host_weight_only(void* pipeline, int layout, const void* x_ho
     cudaGetLastError();
     return qmm::fail(QMM_ERR_DEVICE, "host_weight_only: copy-in: %s", cudaGetErrorString(e));
   }
-  int rc;
+  int wbits, blockwise;
   switch (layout) {
-    case QMM_HOST_W4_BLOCKWISE_PACKED:
-      rc = qmm_w4a16_blockwise_packed(p->xd[slot], x_dtype, static_cast<const uint8_t*>(w), scale, zp, p->yd[slot], out_dtype, M, N, K,
-                                      block_size, variant, p->s_k);
-      break;
-    case QMM_HOST_W4_PERCHANNEL_PACKED:
-      rc = qmm_w4a16_perchannel_packed(p->xd[slot], x_dtype, static_cast<const uint8_t*>(w), scale, zp, p->yd[slot], out_dtype, M, N, K,
-                                       variant, p->s_k);
-      break;
-    case QMM_HOST_W8_PERCHANNEL:
-      rc = qmm_w8a16_perchannel(p->xd[slot], x_dtype, static_cast<const int8_t*>(w), scale, zp, p->yd[slot], out_dtype, M, N, K, variant,
-                                p->s_k);
-      break;
-    case QMM_HOST_W8_BLOCKWISE_KMINOR:
-      rc = qmm_w8a16_blockwise(p->xd[slot], x_dtype, static_cast<const int8_t*>(w), scale, zp, p->yd[slot], out_dtype, M, N, K, block_size,
-                               variant, p->s_k);
-      break;
-    default:
-      return qmm::fail(QMM_ERR_UNSUPPORTED, "host_weight_only: unknown weight layout %d", layout);
+    case QMM_HOST_W4_BLOCKWISE_PACKED: wbits = 4; blockwise = 1; break;
+    case QMM_HOST_W4_PERCHANNEL_PACKED: wbits = 4; blockwise = 0; break;
+    case QMM_HOST_W8_PERCHANNEL: wbits = 8; blockwise = 0; break;
+    case QMM_HOST_W8_BLOCKWISE_KMINOR: wbits = 8; blockwise = 1; break;
+    default: return qmm::fail(QMM_ERR_UNSUPPORTED, "host_weight_only: unknown weight layout %d", layout);
   }
+  if (blockwise && block_size <= 0) return qmm::fail(QMM_ERR_BAD_SHAPE, "host_weight_only: blockwise layout needs block_size > 0");
+  const size_t ws_need = M <= 64 ? qmm_weight_only_workspace_size(M, K) : 0;
+  const bool ws_ok = ws_need > 0 && ws_need <= p->ws_bytes;
+  const int rc = qmm_weight_only(wbits, p->xd[slot], x_dtype, w, scale, zp, p->yd[slot], out_dtype, M, N, K, blockwise ? block_size : 0,
+                                 variant, ws_ok ? p->ws : nullptr, ws_ok ? p->ws_bytes : 0, p->s_k);
   if (rc != QMM_OK) return rc;
   e = cudaEventRecord(p->ev_k[slot], p->s_k);
   if (e == cudaSuccess) e = cudaStreamWaitEvent(p->s_out, p->ev_k[slot], 0);

@@ -36,12 +36,6 @@ bool gemv_nk_supported(int wbits, int64_t M, int64_t N, int64_t K, int64_t block
 int launch_gemv_nk(int wbits, const void* x, int x_dt, const void* w, const float* scale,
                    const float* zp, void* out, int out_dt, int64_t M, int64_t N, int64_t K,
                    int64_t block_size, cudaStream_t st);
-// Decode kernel for the reference's blockwise layout [S,bs,N].
-bool gemv_sbn_supported(int64_t M, int64_t N, int64_t K, int64_t block_size, const void* w);
-int launch_gemv_sbn(const void* x, int x_dt, const int8_t* w, const float* scale, const float* zp,
-                    void* out, int out_dt, int64_t M, int64_t N, int64_t K, int64_t block_size,
-                    cudaStream_t st);
-
 // ---- decode_mma.cu ------------------------------------------------------------------------
 // Decode kernel: weights dequantised in registers and fed to warp-level MMAs (M <= 32, bf16/f16
 // activations, no zero point).  block_size == 0 means per-channel scales.
@@ -66,6 +60,21 @@ bool decode_tc_supported(int wbits, int64_t M, int64_t N, int64_t K, int64_t blo
                          const void* w, bool has_zp);
 int launch_decode_tc(int wbits, const void* x, int x_dt, const void* w, const float* scale, void* out, int out_dt,
                      int64_t M, int64_t N, int64_t K, int64_t block_size, cudaStream_t st);
+
+// ---- limb_gemm.cu (tcgen05 kind::i8 on unconverted weights; activations split into int8 limbs) ----------
+// Weight-only linear for 1 <= M <= 64 (bf16/f16/f32 activations, no zero point): stream-K over all SMs, needs
+// limb_tc_workspace_bytes(M, K) bytes of caller scratch whose first 1024 bytes are zero before the first use (the
+// kernel leaves them zero).  gate_up as in launch_decode_mma.
+constexpr int kLimbMaxCtas = 192;
+size_t limb_tc_workspace_bytes(int64_t M, int64_t K);
+bool limb_tc_shape_ok(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size, int x_dt, bool has_zp);
+bool limb_tc_supported(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size, const void* x, int x_dt,
+                       const void* w, bool has_zp);
+// AUTO's shape rule: true where this kernel is the fastest measured choice.
+bool limb_tc_preferred(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size);
+int launch_limb_tc(int wbits, const void* x, int x_dt, const void* w, const float* scale, void* out, int out_dt, int64_t M,
+                   int64_t N, int64_t K, int64_t block_size, int gate_up, void* workspace, size_t workspace_bytes,
+                   cudaStream_t st);
 
 // ---- peer_reduce.cu -----------------------------------------------------------------------
 // One-shot all-reduce of fp32 partial results that every rank keeps in peer-mapped memory.

@@ -1,0 +1,960 @@
+// Weight-only (W8A16 / W4A16) linear for decode and small prefill batches on the integer tensor cores,
+// with NO weight conversion on the CUDA cores:
+//
+//   out[m,n] = sum_b scale[b,n] * (sum_{k in block b} x[m,k] * w[n,k])          (per-channel: one block)
+//
+// Replaces the reference's mixed-dtype dot and blockwise einsum pair
+// (torch_xla/experimental/xla_quantized_matmul.py:113-114, :120-124, :152-170).
+//
+// Idea.  The weights are already integers; only the activations are floating point.  Each activation row is
+// rewritten, exactly, as a fixed-point number relative to the row's largest exponent,
+//     x[m,k] = X[m,k] * 2^(e_m - 21),   X integer, |X| < 2^22,   X = l0 + 256*l1 + 65536*l2,  l_i in [-128,127]
+// (a bf16/f16 value whose exponent is within 14 of the row maximum is represented exactly; smaller ones are rounded
+// at 2^-22 of the row maximum, the error scale of an fp32 accumulation).  The three int8 "limb" rows of a token
+// become three columns of the MMA's token operand, so that
+//     sum_k x[m,k] w[n,k] = 2^(e_m-21) * ( A0 + 256*A1 + 65536*A2 ),   A_i = sum_k l_i[m,k] * w[n,k]   (int32, exact)
+// and the int8 weights go TMA -> shared memory -> tcgen05.mma.kind::i8 untouched.  int4 weights (two's complement
+// nibbles, two per byte) only need their nibbles moved into the high half of a byte (value * 16 as int8: three
+// integer instructions per eight weights instead of the nine-plus-four of an int4 -> bf16 conversion); the factor
+// 16 is folded into the per-token power of two.
+//
+// Structure.  "Swap-AB": 128 weight rows are the MMA's M side, the limb columns (3 per token, 16..192) its N side.
+//   split_rows_kernel   one CTA per token: row maximum, limbs (in the k order the weight operand uses), 2^(e-21)
+//   limb_tc_kernel      one CTA per SM, stream-K: the (row tile, 256-value K slot) units are dealt to the CTAs in
+//                       equal contiguous shares, so every SM streams the same number of weight bytes whatever N and
+//                       K; a tile that spans several CTAs is summed by the CTA that holds its first K range from
+//                       fp32 partials the others leave in global scratch (fixed order: deterministic)
+//     warp 0            TMA producer of weight bytes (two 128-row x 128-byte tiles per slot, 128-byte swizzle)
+//     warp 1            MMA issuer: eight tcgen05.mma.kind::i8 (M128 x N=NCOLS x K32) per slot behind ONE barrier
+//                       wait and ONE commit; one TMEM accumulator per scale block, several blocks in flight
+//     warp 2            TMA producer of the limb tiles (two NCOLS-row x 128-byte tiles per slot)
+//     warps 4..7        drain: tcgen05.ld a block's int32 sums, recombine the limbs in fp32, fold with scale[b,n]
+//     warps 8..15       (int4 only) nibble -> byte expansion, raw ring -> operand slots; two groups of four warps
+//                       take alternate slots
+// Weight bytes in flight per SM = the depth of the TMA ring (64-190 KB), independent of registers and occupancy.
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "ptx_sm100.cuh"
+
+namespace qmm {
+
+namespace {
+
+constexpr int BMW = 128;                    // weight rows per tile (UMMA M)
+constexpr int kTileK = 128;                 // k values per operand tile = one 128-byte swizzle row of int8
+constexpr int kSlotK = 256;                 // k values per ring slot: two operand tiles
+constexpr int UMMA_K = 32;                  // kind::i8
+constexpr uint32_t kATile = BMW * 128;      // 16 KB
+constexpr uint32_t kASlot = 2 * kATile;     // 32 KB
+constexpr uint32_t kRawBytes = BMW * 128;   // one raw int4 slot: 128 rows x 256 nibbles
+constexpr int kDrainWarp0 = 4;
+constexpr int kConvWarp0 = 8;
+constexpr int kMaxAcc = 8;
+constexpr uint32_t kSmemBudget = 227 * 1024 - 1024 /*alignment*/ - 1024 /*barriers*/;
+
+// Optional per-role cycle accounting of CTA 0 (compile with -DQMM_LIMB_DBG; never in the shipped build).
+#ifdef QMM_LIMB_DBG
+}  // namespace
+__device__ long long g_limb_dbg[64];
+namespace {
+#define DBG_DECL long long dbg_t = 0, dbg_w[4] = {0, 0, 0, 0}; const long long dbg_t0 = clock64(); (void)dbg_t
+#define DBG_BEGIN() dbg_t = clock64()
+#define DBG_END(i) dbg_w[i] += clock64() - dbg_t
+#define DBG_FLUSH(base)                                                  \
+  if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) {                      \
+    for (int i_ = 0; i_ < 4; ++i_) g_limb_dbg[(base) + i_] = dbg_w[i_];  \
+    g_limb_dbg[(base) + 4] = clock64() - dbg_t0;                         \
+  }
+#else
+#define DBG_DECL
+#define DBG_BEGIN()
+#define DBG_END(i)
+#define DBG_FLUSH(base)
+#endif
+
+enum LimbErr : uint32_t { kErrPartialWait = 9 };  // owner CTA never saw a partial tile arrive
+
+// How the K axis maps onto accumulators.
+enum Mode : int {
+  kPerChannel = 0,  // one accumulation per (tile, K range of the CTA)
+  kBlock128 = 1,    // scale blocks of 128: two blocks per slot
+  kBlockSlots = 2,  // scale blocks of spb whole slots
+};
+
+struct Params {
+  const float* scale;  // [N] or [S,N]
+  const float* pw;     // [M]: 2^(e_m - 21) (times 1/16 for int4 weights)
+  void* out;
+  int out_dt;
+  int M;
+  int64_t N;
+  int tiles;   // ceil(N / 128)
+  int slots;   // K slots per tile
+  int spu;     // slots per scheduling unit (= slots per scale block in kBlockSlots mode, else 1)
+  int ut;      // units per tile
+  int mode;
+  int S;       // scale blocks
+  long long units;
+  float* partial;   // [grid][MT][128] fp32
+  uint32_t* flags;  // [grid], zero between launches
+  uint32_t* err_word;
+  int gate_up;
+};
+
+template <int WBITS, int NCOLS>
+struct Cfg {
+  static constexpr uint32_t kBTile = NCOLS * 128;
+  // int4 with up to 96 limb columns: the expanded weight operand lives in tensor memory (64 columns per slot, four
+  // slots in the upper half of TMEM) and never touches shared memory; the ring slots then hold limb tiles only
+  static constexpr bool kATmem = WBITS == 4 && NCOLS <= 96;
+  static constexpr int kATmemCol0 = 256, kATmemSlotCols = 64;
+  static constexpr uint32_t kAInSlot = kATmem ? 0 : kASlot;
+  static constexpr uint32_t kSlot = kAInSlot + 2 * kBTile;   // [A tile 0 | A tile 1 |] B tile 0 | B tile 1
+  static constexpr int kSlots = kATmem ? 4 : (WBITS == 4 ? 2 : std::min<int>(6, kSmemBudget / kSlot));
+  static constexpr int kRawFit = WBITS == 4 ? (int)((kSmemBudget - kSlots * kSlot) / kRawBytes) : 0;
+  static constexpr int kRaw = WBITS == 4 ? std::min(10, kRawFit & ~1) : 0;   // even: each group of expanding warps owns alternate slots
+  static constexpr int kAccCols = kATmem ? kATmemCol0 : 512;
+  static constexpr int kRegions = std::min(2 * kMaxAcc, kAccCols / NCOLS);   // accumulators that fit in TMEM
+  // two accumulators of a block-128 slot share one hand-over between MMA issuer and drain warps
+  static constexpr bool kPair = kRegions >= 4;
+  static constexpr int kTokens = NCOLS / 3;
+  static constexpr int kThreads = WBITS == 4 ? 512 : 256;
+  static constexpr size_t kSmem = 1024 + (size_t)kRaw * kRawBytes + (size_t)kSlots * kSlot + 1024;
+  static_assert(kSlots >= 2 && (WBITS == 8 || (kRaw >= 2 && kSlots % 2 == 0)), "ring depths");
+  static_assert(kRegions >= 2, "two accumulators, so that drain and MMA overlap");
+  static_assert(kSmem <= 227 * 1024, "shared memory budget");
+};
+
+// The (tile, unit range) fragments of this CTA's share of the stream-K schedule, in order.
+struct FragIter {
+  long long u, hi;
+  int ut;
+  __device__ FragIter(const Params& p) : ut(p.ut) {
+    const long long G = gridDim.x;
+    u = (long long)blockIdx.x * p.units / G;
+    hi = (long long)(blockIdx.x + 1) * p.units / G;
+  }
+  __device__ bool next(int& tile, int& u0, int& u1) {
+    if (u >= hi) return false;
+    tile = (int)(u / ut);
+    u0 = (int)(u - (long long)tile * ut);
+    const long long rem = hi - u;
+    u1 = (int)(rem < (long long)(ut - u0) ? u0 + rem : ut);
+    u += u1 - u0;
+    return true;
+  }
+};
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void drain_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+__device__ __forceinline__ float silu_mul(float gate, float up) { return gate / (1.f + expf(-gate)) * up; }
+__device__ __forceinline__ int64_t gate_up_column(int64_t n) { return ((n >> 4) << 3) + (n & 7); }
+
+// ---- activation rows -> int8 limbs -------------------------------------------------------------------------------
+// Order of k inside the operand rows.  int8 weights: natural.  int4 weights: the nibble expansion emits, per raw
+// 16-byte chunk (32 nibbles, k = 32c + 8j + i), the 16 even-k values and then the 16 odd-k values, so value k sits at
+// 32c + 16*(i & 1) + 4j + i/2; the limb rows are written in the same order.
+template <typename XT>
+__device__ __forceinline__ void load8(const XT* p, float* v);
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float* v) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float* v) {
+  const uint4 a = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+template <>
+__device__ __forceinline__ void load8<__half>(const __half* p, float* v) {
+  const uint4 a = *reinterpret_cast<const uint4*>(p);
+  const __half2* h = reinterpret_cast<const __half2*>(&a);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(h[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+
+// One CTA per token row.  xl: [3*M][K] int8, row 3*m + l = limb l of token m; pw[m] = 2^(e_m - 21) * pw_mul.
+// A row with a non-finite entry gets pw = NaN (its outputs are NaN); an all-zero row gets zeros.
+template <typename XT>
+__global__ void __launch_bounds__(1024) split_rows_kernel(const XT* __restrict__ x, int8_t* __restrict__ xl, float* __restrict__ pw,
+                                                          int64_t K, int perm4, float pw_mul) {
+  __shared__ uint32_t s_max[32];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // x may come from the previous kernel of the stream
+  const int m = blockIdx.x;
+  const XT* xr = x + (int64_t)m * K;
+  const int64_t groups = K >> 3;
+  uint32_t mx = 0;
+  for (int64_t gi = threadIdx.x; gi < groups; gi += blockDim.x) {
+    float v[8];
+    load8<XT>(xr + gi * 8, v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) mx = max(mx, __float_as_uint(v[i]) & 0x7fffffffu);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    uint32_t t = threadIdx.x < (blockDim.x >> 5) ? s_max[threadIdx.x] : 0u;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t = max(t, __shfl_xor_sync(0xffffffffu, t, o));
+    if (threadIdx.x == 0) s_max[0] = t;
+  }
+  __syncthreads();
+  mx = s_max[0];
+  int e = (int)(mx >> 23) - 127;  // exponent of the row maximum
+  const bool finite = e < 128;
+  if (e < -100) e = -100;         // zero / denormal rows: any small exponent represents them exactly enough
+  const float mult = finite ? __uint_as_float((uint32_t)(21 - e + 127) << 23) : 0.f;  // 2^(21-e)
+  if (threadIdx.x == 0) pw[m] = finite ? __uint_as_float((uint32_t)(e - 21 + 127) << 23) * pw_mul : __uint_as_float(0x7fc00000u);
+  int8_t* r0 = xl + (int64_t)(3 * m) * K;
+  int8_t* r1 = r0 + K;
+  int8_t* r2 = r1 + K;
+  for (int64_t gi = threadIdx.x; gi < groups; gi += blockDim.x) {
+    float v[8];
+    load8<XT>(xr + gi * 8, v);
+    uint32_t l0[2] = {0, 0}, l1[2] = {0, 0}, l2[2] = {0, 0};  // bytes of limb l for k = 8*gi + i, packed in k order
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int X = __float2int_rn(v[i] * mult);
+      const int a0 = (int)(int8_t)(X & 0xff);
+      const int X1 = (X - a0) >> 8;
+      const int a1 = (int)(int8_t)(X1 & 0xff);
+      const int a2 = (X1 - a1) >> 8;
+      l0[i >> 2] |= (uint32_t)(a0 & 0xff) << (8 * (i & 3));
+      l1[i >> 2] |= (uint32_t)(a1 & 0xff) << (8 * (i & 3));
+      l2[i >> 2] |= (uint32_t)(a2 & 0xff) << (8 * (i & 3));
+    }
+    if (!perm4) {
+      const int64_t o = gi * 8;
+      *reinterpret_cast<uint2*>(r0 + o) = make_uint2(l0[0], l0[1]);
+      *reinterpret_cast<uint2*>(r1 + o) = make_uint2(l1[0], l1[1]);
+      *reinterpret_cast<uint2*>(r2 + o) = make_uint2(l2[0], l2[1]);
+    } else {
+      // k = 32*c + 8*j + i -> even i at 32*c + 4*j + i/2, odd i at 32*c + 16 + 4*j + i/2
+      const int64_t base = (gi >> 2) * 32 + (gi & 3) * 4;
+      auto evens = [](const uint32_t* l) { return __byte_perm(l[0], l[1], 0x6420); };
+      auto odds = [](const uint32_t* l) { return __byte_perm(l[0], l[1], 0x7531); };
+      *reinterpret_cast<uint32_t*>(r0 + base) = evens(l0);
+      *reinterpret_cast<uint32_t*>(r0 + base + 16) = odds(l0);
+      *reinterpret_cast<uint32_t*>(r1 + base) = evens(l1);
+      *reinterpret_cast<uint32_t*>(r1 + base + 16) = odds(l1);
+      *reinterpret_cast<uint32_t*>(r2 + base) = evens(l2);
+      *reinterpret_cast<uint32_t*>(r2 + base + 16) = odds(l2);
+    }
+  }
+}
+
+// ---- the stream-K tensor-core kernel -----------------------------------------------------------------------------
+// One accumulator (NCOLS int32 columns of this thread's TMEM lane) -> limbs recombined in fp32, times sc, into total.
+template <int NCOLS, int MT, typename Release>
+__device__ __forceinline__ void fold_region(uint32_t taddr, float sc, float (&total)[MT], bool release_after, Release release) {
+  constexpr int kChunks = (NCOLS + 47) / 48;
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
+    uint32_t r[48];
+#pragma unroll
+    for (int j = 0; j < 3; ++j)
+      if (c * 48 + 16 * j < NCOLS) ptx::tmem_ld_32x32b_x16(taddr + c * 48 + 16 * j, r + 16 * j);
+    ptx::tmem_ld_wait();
+    if (c == kChunks - 1 && release_after) release();  // the accumulator's last values are in registers
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      if (c * 16 + t < MT) {
+        const float f0 = __int2float_rn((int)r[3 * t]), f1 = __int2float_rn((int)r[3 * t + 1]),
+                    f2 = __int2float_rn((int)r[3 * t + 2]);
+        total[c * 16 + t] = fmaf(sc, fmaf(f2, 65536.f, fmaf(f1, 256.f, f0)), total[c * 16 + t]);
+      }
+    }
+  }
+}
+
+template <int WBITS, int NCOLS>
+__global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, 1)
+    limb_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const Params p) {
+  using C = Cfg<WBITS, NCOLS>;
+  constexpr int kRaw = C::kRaw, kSlots = C::kSlots;
+  constexpr uint32_t kBTile = C::kBTile, kSlot = C::kSlot;
+  constexpr int MT = C::kTokens;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* raw_base = smem;
+  uint8_t* slot_base = raw_base + (size_t)kRaw * kRawBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(slot_base + (size_t)kSlots * kSlot);
+  uint64_t* raw_full = bars;                       // [kRaw]    TMA bytes
+  uint64_t* raw_empty = raw_full + (kRaw ? kRaw : 1);  // [kRaw]    4 expanding warps
+  uint64_t* full = raw_empty + (kRaw ? kRaw : 1);      // [kSlots]  int8: both TMA producers; int4: 4 expanding warps + limb producer
+  uint64_t* empty = full + kSlots;                 // [kSlots]  tcgen05.commit
+  uint64_t* acc_full = empty + kSlots;             // [kMaxAcc] tcgen05.commit
+  uint64_t* acc_empty = acc_full + kMaxAcc;        // [kMaxAcc] 4 drain warps
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + kMaxAcc);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef QMM_LIMB_DBG
+  const long long dbg_k0 = clock64();
+  const unsigned long long dbg_g0 = ptx::globaltimer_ns();
+#endif
+  // accumulators per hand-over and hand-over buffers in the TMEM ring
+  const int gph = (p.mode == kBlock128 && C::kPair) ? 2 : 1;
+  const int nacc = min(kMaxAcc, C::kRegions / gph);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kRaw; ++s) {
+      ptx::mbar_init(&raw_full[s], 1);
+      ptx::mbar_init(&raw_empty[s], 4);
+    }
+    for (int s = 0; s < kSlots; ++s) {
+      ptx::mbar_init(&full[s], WBITS == 4 ? 5 : 2);
+      ptx::mbar_init(&empty[s], 1);
+    }
+    for (int s = 0; s < kMaxAcc; ++s) {
+      ptx::mbar_init(&acc_full[s], 1);
+      ptx::mbar_init(&acc_empty[s], 4);
+    }
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&map_w);
+    ptx::prefetch_tensormap(&map_x);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, 512);
+    ptx::tmem_relinquish();
+  }
+  ptx::tcgen05_fence_before();
+  __syncthreads();
+  ptx::tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // The next kernel of the stream may start its own set-up now; it touches nothing of ours before its own wait.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  if (warp == 0) {
+    // ---------------- weight producer: needs nothing from earlier kernels, so it does not wait for them ----------------
+    if (lane == 0) {
+      FragIter it(p);
+      DBG_DECL;
+      int tile, u0, u1, slot = 0;
+      uint32_t ph = 0;
+      while (it.next(tile, u0, u1)) {
+        const int s0 = u0 * p.spu, s1 = min(p.slots, u1 * p.spu);
+        for (int s = s0; s < s1; ++s) {
+          if constexpr (WBITS == 8) {
+            DBG_BEGIN();
+            ptx::mbar_wait<32>(&empty[slot], ph ^ 1, abort_flag, p.err_word, ptx::kErrWaitEmpty);
+            DBG_END(0);
+            uint8_t* dst = slot_base + (size_t)slot * kSlot;
+            ptx::mbar_expect_tx(&full[slot], kASlot);
+            ptx::tma_load_2d(dst, &map_w, &full[slot], s * kSlotK, tile * BMW);
+            ptx::tma_load_2d(dst + kATile, &map_w, &full[slot], s * kSlotK + kTileK, tile * BMW);
+            if (++slot == kSlots) { slot = 0; ph ^= 1; }
+          } else {
+            DBG_BEGIN();
+            ptx::mbar_wait<32>(&raw_empty[slot], ph ^ 1, abort_flag, p.err_word, ptx::kErrWaitEmpty);
+            DBG_END(0);
+            ptx::mbar_expect_tx(&raw_full[slot], kRawBytes);
+            ptx::tma_load_2d(raw_base + (size_t)slot * kRawBytes, &map_w, &raw_full[slot], s * 128, tile * BMW);
+            if (++slot == kRaw) { slot = 0; ph ^= 1; }
+          }
+        }
+      }
+      DBG_FLUSH(0);
+    }
+  } else if (warp == 2) {
+    // ---------------- limb tile producer ----------------
+    if (lane == 0) {
+      asm volatile("griddepcontrol.wait;" ::: "memory");  // the limbs are written by the kernel before this one
+      FragIter it(p);
+      DBG_DECL;
+      int tile, u0, u1, slot = 0;
+      uint32_t ph = 0;
+      while (it.next(tile, u0, u1)) {
+        const int s0 = u0 * p.spu, s1 = min(p.slots, u1 * p.spu);
+        for (int s = s0; s < s1; ++s) {
+          DBG_BEGIN();
+          ptx::mbar_wait<32>(&empty[slot], ph ^ 1, abort_flag, p.err_word, ptx::kErrWaitEmpty);
+          DBG_END(0);
+          uint8_t* dst = slot_base + (size_t)slot * kSlot + C::kAInSlot;
+          ptx::mbar_expect_tx(&full[slot], 2 * kBTile);
+          ptx::tma_load_2d(dst, &map_x, &full[slot], s * kSlotK, 0);
+          ptx::tma_load_2d(dst + kBTile, &map_x, &full[slot], s * kSlotK + kTileK, 0);
+          if (++slot == kSlots) { slot = 0; ph ^= 1; }
+        }
+      }
+      DBG_FLUSH(8);
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer: the whole warp walks the loop, lane 0's instructions take effect ----------------
+    constexpr uint32_t idesc = ptx::make_idesc(/*s32*/ 2, /*s8*/ 1, /*s8*/ 1, BMW, NCOLS);
+    const uint32_t leader = lane == 0 ? 1u : 0u;
+    const uint32_t desc_hi = (uint32_t)(ptx::make_sw128_kmajor_desc(0) >> 32);
+    const uint32_t lo0 = (uint32_t)ptx::make_sw128_kmajor_desc(ptx::smem_u32(slot_base));
+    FragIter it(p);
+    DBG_DECL;
+    int tile, u0, u1;
+    int slot = 0, buf = 0;
+    uint32_t ph = 0, pacc = 0;
+    uint32_t lo = lo0;
+    // the four MMAs of operand tile t of the current slot into accumulator d
+    auto issue_tile = [&](uint32_t d, int t, uint32_t accum) {
+      const uint32_t a_lo = lo + t * (kATile >> 4), b_lo = lo + (C::kAInSlot >> 4) + t * (kBTile >> 4);
+#pragma unroll
+      for (int k = 0; k < kTileK / UMMA_K; ++k) {
+        const uint64_t bd = ((uint64_t)desc_hi << 32) | (uint64_t)(b_lo + k * (UMMA_K >> 4));
+        if constexpr (C::kATmem) {
+          // operand rows = TMEM lanes; one K=32 step = 8 columns = one expanded 16-byte chunk of nibbles
+          const uint32_t a_tm = tmem_base + C::kATmemCol0 + slot * C::kATmemSlotCols + (4 * t + k) * 8;
+          ptx::mma_i8_ts_pred(d, a_tm, bd, idesc, accum | (uint32_t)k, leader);
+        } else {
+          const uint64_t ad = ((uint64_t)desc_hi << 32) | (uint64_t)(a_lo + k * (UMMA_K >> 4));
+          ptx::mma_i8_ss_pred(d, ad, bd, idesc, accum | (uint32_t)k, leader);
+        }
+      }
+    };
+    auto wait_acc = [&]() {
+      DBG_BEGIN();
+      ptx::mbar_wait(&acc_empty[buf], pacc ^ 1, abort_flag, p.err_word, ptx::kErrWaitTmemEmpty);
+      DBG_END(0);
+      ptx::tcgen05_fence_after();
+    };
+    auto next_acc = [&]() {
+      ptx::mma_commit_pred(&acc_full[buf], leader);
+      if (++buf == nacc) { buf = 0; pacc ^= 1; }
+    };
+    auto wait_slot = [&]() {
+      DBG_BEGIN();
+      ptx::mbar_wait(&full[slot], ph, abort_flag, p.err_word, ptx::kErrWaitFull);
+      DBG_END(1);
+      ptx::tcgen05_fence_after();
+    };
+    auto next_slot = [&]() {
+      ptx::mma_commit_pred(&empty[slot], leader);  // frees the slot once the MMAs issued so far have read it
+      lo += kSlot >> 4;
+      if (++slot == kSlots) { slot = 0; ph ^= 1; lo = lo0; }
+    };
+    while (it.next(tile, u0, u1)) {
+      const int s0 = u0 * p.spu, s1 = min(p.slots, u1 * p.spu);
+      if (p.mode == kBlock128) {
+        for (int s = s0; s < s1; ++s) {
+          if (C::kPair) {
+            wait_acc();
+            wait_slot();
+            const uint32_t d = tmem_base + buf * (2 * NCOLS);
+            issue_tile(d, 0, 0);
+            issue_tile(d + NCOLS, 1, 0);
+            next_slot();
+            next_acc();
+          } else {
+            wait_acc();
+            wait_slot();
+            issue_tile(tmem_base + buf * NCOLS, 0, 0);
+            next_acc();
+            wait_acc();
+            issue_tile(tmem_base + buf * NCOLS, 1, 0);
+            next_slot();
+            next_acc();
+          }
+        }
+      } else {
+        int s = s0;
+        while (s < s1) {
+          const int g_end = p.mode == kBlockSlots ? min(s1, s + p.spu) : s1;  // fragments start on block boundaries
+          wait_acc();
+          const uint32_t d = tmem_base + buf * NCOLS;
+          uint32_t accum = 0;
+          for (; s < g_end; ++s) {
+            wait_slot();
+            issue_tile(d, 0, accum);
+            issue_tile(d, 1, 1);
+            accum = 1;
+            next_slot();
+          }
+          next_acc();
+        }
+      }
+    }
+    DBG_FLUSH(16);
+  } else if (warp >= kDrainWarp0 && warp < kDrainWarp0 + 4) {
+    // ---------------- drain: thread = one weight row n (its TMEM lane) ----------------
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // pw, the scratch and `out` belong to earlier kernels until here
+    const int quad = warp & 3;
+    const int rl = quad * 32 + lane;  // row inside the tile
+    const int dt = threadIdx.x - kDrainWarp0 * 32;  // 0..127 among the drain threads
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const long long G = gridDim.x;
+    FragIter it(p);
+    DBG_DECL;
+    int tile, u0, u1, buf = 0;
+    uint32_t pacc = 0;
+    __shared__ int s_npart, s_ready;
+    auto wait_acc = [&]() {
+      DBG_BEGIN();
+      ptx::mbar_wait_warp<32>(&acc_full[buf], pacc, abort_flag, p.err_word, ptx::kErrWaitTmemFull);
+      DBG_END(0);
+      ptx::tcgen05_fence_after();
+    };
+    auto release = [&]() {
+      ptx::tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
+    };
+    auto next_acc = [&]() {
+      if (++buf == nacc) { buf = 0; pacc ^= 1; }
+    };
+    while (it.next(tile, u0, u1)) {
+      const int s0 = u0 * p.spu, s1 = min(p.slots, u1 * p.spu);
+      const int64_t n = (int64_t)tile * BMW + rl;
+      const bool n_ok = n < p.N;
+      const bool first = u0 == 0, last = u1 == p.ut;
+      float total[MT];
+#pragma unroll
+      for (int t = 0; t < MT; ++t) total[t] = 0.f;
+      // A tile this CTA starts and others continue: their partial sums are usually there already (every CTA works on
+      // its share of a started tile first), so they are fetched now, under the K loop, when all of them have landed;
+      // otherwise after it.  The order of the additions is the same either way.
+      int np = 0;
+      bool fetched = false;
+      auto add_partials = [&]() {
+        for (int j = 0; j < np; ++j) {
+          const float* src = p.partial + ((size_t)(blockIdx.x + 1 + j) * MT) * BMW + rl;
+#pragma unroll
+          for (int t = 0; t < MT; ++t)
+            if (t < p.M) total[t] += __ldcg(src + t * BMW);
+        }
+        drain_bar();
+        for (int j = dt; j < np; j += 128) p.flags[blockIdx.x + 1 + j] = 0u;  // clean for the next launch
+      };
+      if (first && !last) {
+        if (dt == 0) {
+          int cnt = 0;
+          for (long long c2 = blockIdx.x + 1; c2 < G; ++c2) {
+            if (c2 * p.units / G >= (long long)(tile + 1) * p.ut) break;
+            ++cnt;
+          }
+          s_npart = cnt;
+          s_ready = 1;
+        }
+        drain_bar();
+        np = s_npart;
+        for (int j = dt; j < np; j += 128)
+          if (ld_acquire_gpu(p.flags + blockIdx.x + 1 + j) == 0u) s_ready = 0;
+        drain_bar();
+        fetched = s_ready != 0;
+        if (fetched) add_partials();
+      }
+      // block scales are fetched four blocks ahead: a load issued in the iteration that uses it would put an L2
+      // round trip into every block's drain
+      constexpr int kAhead = 4;
+      float scq[kAhead];
+      int b_next = p.mode == kBlock128 ? 2 * s0 : (p.mode == kBlockSlots ? s0 / p.spu : 0);
+      auto fetch_scale = [&]() {
+        const float v = (p.mode != kPerChannel && n_ok && b_next < p.S) ? __ldg(p.scale + (int64_t)b_next * p.N + n) : 0.f;
+        ++b_next;
+        return v;
+      };
+      auto pop_scale = [&]() {
+        const float v = scq[0];
+#pragma unroll
+        for (int i = 0; i + 1 < kAhead; ++i) scq[i] = scq[i + 1];
+        scq[kAhead - 1] = fetch_scale();
+        return v;
+      };
+#pragma unroll
+      for (int i = 0; i < kAhead; ++i) scq[i] = fetch_scale();
+      if (p.mode == kBlock128) {
+        for (int s = s0; s < s1; ++s) {
+          if (C::kPair) {
+            wait_acc();
+            DBG_BEGIN();
+            const uint32_t a = lane_addr + buf * (2 * NCOLS);
+            fold_region<NCOLS, MT>(a, pop_scale(), total, false, release);
+            fold_region<NCOLS, MT>(a + NCOLS, pop_scale(), total, true, release);
+            DBG_END(1);
+            next_acc();
+          } else {
+#pragma unroll 1
+            for (int h = 0; h < 2; ++h) {
+              wait_acc();
+              DBG_BEGIN();
+              fold_region<NCOLS, MT>(lane_addr + buf * NCOLS, pop_scale(), total, true, release);
+              DBG_END(1);
+              next_acc();
+            }
+          }
+        }
+      } else {
+        int s = s0;
+        while (s < s1) {
+          const int g_end = p.mode == kBlockSlots ? min(s1, s + p.spu) : s1;
+          const float sc = p.mode == kPerChannel ? 1.f : pop_scale();
+          wait_acc();
+          DBG_BEGIN();
+          fold_region<NCOLS, MT>(lane_addr + buf * NCOLS, sc, total, true, release);
+          DBG_END(1);
+          next_acc();
+          s = g_end;
+        }
+      }
+      DBG_BEGIN();
+      // ---- end of the fragment ----
+      if (!first) {
+        // a later K range of a tile that another CTA started: leave the partial sums for that CTA
+        float* dst = p.partial + ((size_t)blockIdx.x * MT) * BMW + rl;
+#pragma unroll
+        for (int t = 0; t < MT; ++t)
+          if (t < p.M) __stcg(dst + t * BMW, total[t]);
+        __threadfence();
+        drain_bar();
+        if (dt == 0) st_release_gpu(p.flags + blockIdx.x, 1u);
+        DBG_END(2);
+        continue;
+      }
+      if (!last && !fetched) {
+        // add the partial sums of the CTAs that continue the tile, in CTA order
+        for (int j = dt; j < np; j += 128) {
+          const uint32_t* f = p.flags + blockIdx.x + 1 + j;
+          const long long t0 = clock64();
+          uint32_t spins = 0;
+          while (ld_acquire_gpu(f) == 0u) {
+            if ((++spins & 0xff) == 0 && (*abort_flag || clock64() - t0 > ptx::kWaitLimitCycles)) {
+              *abort_flag = kErrPartialWait;
+              if (p.err_word) atomicCAS(p.err_word, 0u, kErrPartialWait | (blockIdx.x << 8));
+              break;
+            }
+          }
+        }
+        drain_bar();
+        add_partials();
+      }
+      const float ps = (p.mode != kPerChannel || !n_ok) ? 1.f : __ldg(p.scale + n);
+      if (!p.gate_up) {
+#pragma unroll
+        for (int t = 0; t < MT; ++t)
+          if (t < p.M && n_ok) store_from_f32(p.out, (int64_t)t * p.N + n, p.out_dt, total[t] * ps * __ldg(p.pw + t));
+      } else {
+        // rows come in groups of 16: eight gate rows, then the eight up rows of the same outputs
+#pragma unroll
+        for (int t = 0; t < MT; ++t) {
+          const float v = t < p.M ? total[t] * ps * __ldg(p.pw + t) : 0.f;
+          const float u = __shfl_down_sync(0xffffffffu, v, 8);
+          if (t < p.M && n_ok && (rl & 8) == 0)
+            store_from_f32(p.out, (int64_t)t * (p.N >> 1) + gate_up_column(n), p.out_dt, silu_mul(v, u));
+        }
+      }
+      DBG_END(2);
+    }
+    if (warp == kDrainWarp0) { DBG_FLUSH(24); }
+  } else if (WBITS == 4 && warp >= kConvWarp0) {
+    // ---------------- int4: nibble -> high half of a byte (value * 16 as int8); lane = row ----------------
+    // Two groups of four warps; group g expands the slots g, g+2, ... of the CTA's sequence (ring depths are even,
+    // so a ring slot always belongs to the same group).
+    const int grp = (warp - kConvWarp0) >> 2, cw = (warp - kConvWarp0) & 3;
+    const int r = cw * 32 + lane;
+    const uint32_t sw = (uint32_t)(r & 7);
+    const uint32_t raw_row = ptx::smem_u32(raw_base) + r * 128;
+    const uint32_t a_row = ptx::smem_u32(slot_base) + r * 128;
+    FragIter it(p);
+    DBG_DECL;
+    int tile, u0, u1;
+    uint32_t i = 0;  // position in the CTA's slot sequence
+    while (it.next(tile, u0, u1)) {
+      const int s0 = u0 * p.spu, s1 = min(p.slots, u1 * p.spu);
+      for (int s = s0; s < s1; ++s, ++i) {
+        if ((int)(i & 1) != grp) continue;
+        const uint32_t sr = i % kRaw, pr = (i / kRaw) & 1, sa = i % kSlots, pa = (i / kSlots) & 1;
+        DBG_BEGIN();
+        ptx::mbar_wait_warp<32>(&raw_full[sr], pr, abort_flag, p.err_word, ptx::kErrWaitRaw);
+        DBG_END(0);
+        uint4 v[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) v[c] = lds128(raw_row + sr * kRawBytes + (((uint32_t)c ^ sw) << 4));
+        DBG_BEGIN();
+        ptx::mbar_wait_warp<32>(&empty[sa], pa ^ 1, abort_flag, p.err_word, ptx::kErrWaitEmpty);
+        DBG_END(1);
+        if constexpr (C::kATmem) {
+          ptx::tcgen05_fence_after();  // the MMAs that read this TMEM slot last have completed (their commit freed it)
+          const uint32_t t_row = tmem_base + ((uint32_t)(cw * 32) << 16) + C::kATmemCol0 + sa * C::kATmemSlotCols;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const uint4 q = v[c];
+            const uint32_t w8[8] = {(q.x << 4) & 0xF0F0F0F0u, (q.y << 4) & 0xF0F0F0F0u, (q.z << 4) & 0xF0F0F0F0u,
+                                    (q.w << 4) & 0xF0F0F0F0u, q.x & 0xF0F0F0F0u,        q.y & 0xF0F0F0F0u,
+                                    q.z & 0xF0F0F0F0u,        q.w & 0xF0F0F0F0u};
+            ptx::tmem_st_32x32b_x8(t_row + 8 * c, w8);
+          }
+          ptx::tmem_st_wait();
+          ptx::tcgen05_fence_before();
+        } else {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const uint32_t dst = a_row + sa * kSlot + (c >> 2) * kATile;
+            const int cc = c & 3;
+            const uint4 q = v[c];
+            sts128(dst + (((uint32_t)(2 * cc) ^ sw) << 4), (q.x << 4) & 0xF0F0F0F0u, (q.y << 4) & 0xF0F0F0F0u,
+                   (q.z << 4) & 0xF0F0F0F0u, (q.w << 4) & 0xF0F0F0F0u);
+            sts128(dst + (((uint32_t)(2 * cc + 1) ^ sw) << 4), q.x & 0xF0F0F0F0u, q.y & 0xF0F0F0F0u, q.z & 0xF0F0F0F0u,
+                   q.w & 0xF0F0F0F0u);
+          }
+          ptx::fence_proxy_async_smem();  // generic-proxy stores -> visible to the MMA's async proxy
+        }
+        __syncwarp();
+        if (lane == 0) {
+          ptx::mbar_arrive(&full[sa]);
+          ptx::mbar_arrive(&raw_empty[sr]);
+        }
+      }
+    }
+    if (warp == kConvWarp0) { DBG_FLUSH(32); }
+  }
+
+  ptx::tcgen05_fence_before();
+  __syncthreads();
+#ifdef QMM_LIMB_DBG
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    g_limb_dbg[40] = clock64() - dbg_k0;
+    g_limb_dbg[41] = (long long)(ptx::globaltimer_ns() - dbg_g0);
+  }
+#endif
+  if (warp == 1) {
+    ptx::tcgen05_fence_after();
+    ptx::tmem_dealloc(tmem_base, 512);
+  }
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct Scratch {
+  int8_t* limbs;
+  float* pw;
+  float* partial;
+  uint32_t* flags;
+  size_t bytes;
+};
+
+int ncols_for(int64_t M) {
+  if (M <= 5) return 16;
+  if (M <= 10) return 32;
+  if (M <= 16) return 48;
+  if (M <= 32) return 96;
+  if (M <= 64) return 192;
+  return 0;
+}
+
+// Layout of the caller's scratch: [flags: 1 KB][pw][limbs][partial tiles]; the flag words come first so that a
+// caller who clears only the head of the buffer clears them.
+Scratch carve(void* base, int64_t M, int64_t K, int max_ctas) {
+  Scratch s;
+  uint8_t* b = reinterpret_cast<uint8_t*>(base);
+  size_t off = 0;
+  s.flags = reinterpret_cast<uint32_t*>(b + off);
+  off += align_up((size_t)max_ctas * 4, 1024);
+  s.pw = reinterpret_cast<float*>(b + off);
+  off += align_up((size_t)M * 4, 256);
+  s.limbs = reinterpret_cast<int8_t*>(b + off);
+  off += align_up((size_t)3 * M * K, 256);
+  s.partial = reinterpret_cast<float*>(b + off);
+  off += (size_t)max_ctas * (ncols_for(M) / 3) * BMW * 4;
+  s.bytes = off;
+  return s;
+}
+
+template <int WBITS, int NCOLS>
+int launch_cfg(const CUtensorMap& map_w, const CUtensorMap& map_x, const Params& p, int grid, cudaStream_t st) {
+  using C = Cfg<WBITS, NCOLS>;
+  auto kern = limb_tc_kernel<WBITS, NCOLS>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmem);
+    if (e != cudaSuccess) return fail(QMM_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    if (dev >= 0 && dev < 64) attr_set[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(C::kThreads);
+  cfg.dynamicSmemBytes = C::kSmem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_w, map_x, p);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(QMM_ERR_LAUNCH, "limb_tc_kernel launch: %s", cudaGetErrorString(e));
+  }
+  return check_launch("limb_tc_kernel");
+}
+
+template <int WBITS>
+int launch_ncols(int ncols, const CUtensorMap& map_w, const CUtensorMap& map_x, const Params& p, int grid, cudaStream_t st) {
+  switch (ncols) {
+    case 16: return launch_cfg<WBITS, 16>(map_w, map_x, p, grid, st);
+    case 32: return launch_cfg<WBITS, 32>(map_w, map_x, p, grid, st);
+    case 48: return launch_cfg<WBITS, 48>(map_w, map_x, p, grid, st);
+    case 96: return launch_cfg<WBITS, 96>(map_w, map_x, p, grid, st);
+    default: return launch_cfg<WBITS, 192>(map_w, map_x, p, grid, st);
+  }
+}
+
+template <typename XT>
+cudaError_t launch_split(const void* x, int8_t* xl, float* pw, int64_t M, int64_t K, int perm4, float pw_mul, cudaStream_t st) {
+  int threads = (int)std::min<int64_t>(1024, std::max<int64_t>(64, align_up((size_t)(K / 8), 32)));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)M);
+  cfg.blockDim = dim3((unsigned)threads);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, split_rows_kernel<XT>, reinterpret_cast<const XT*>(x), xl, pw, K, perm4, pw_mul);
+}
+
+}  // namespace
+
+size_t limb_tc_workspace_bytes(int64_t M, int64_t K) {
+  if (M < 1 || ncols_for(M) == 0 || K < 1) return 0;
+  return carve(nullptr, M, K, kLimbMaxCtas).bytes;
+}
+
+bool limb_tc_shape_ok(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size, int x_dt, bool has_zp) {
+  if (has_zp) return false;
+  if (x_dt != QMM_BF16 && x_dt != QMM_F16 && x_dt != QMM_F32) return false;
+  if (M < 1 || ncols_for(M) == 0 || N < 1 || K < 128) return false;
+  if (wbits == 8 ? (K % 16 != 0) : (K % 32 != 0)) return false;  // TMA row pitches of the weights and the limbs
+  // scale blocks of 128 (two per slot) or of whole 256-value slots
+  if (block_size > 0 && ((block_size != kTileK && block_size % kSlotK != 0) || K % block_size != 0)) return false;
+  // one int32 accumulation runs over a scale block (all of K per-channel): |limb * weight| <= 2^14 per term
+  if ((block_size > 0 ? block_size : K) > (1 << 16)) return false;
+  if (N > (1LL << 30) || K > (1LL << 24)) return false;
+  return true;
+}
+
+bool limb_tc_supported(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size, const void* x, int x_dt, const void* w,
+                       bool has_zp) {
+  if (!limb_tc_shape_ok(wbits, M, N, K, block_size, x_dt, has_zp)) return false;
+  if (!aligned(x, 16) || !aligned(w, 16)) return false;
+  return device_is_sm100();
+}
+
+bool limb_tc_preferred(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size) {
+  (void)wbits; (void)M; (void)block_size;
+  return N * K >= (1 << 20);  // below ~1 M weights the launch is latency-bound and the register-dequant kernel wins
+}
+
+int launch_limb_tc(int wbits, const void* x, int x_dt, const void* w, const float* scale, void* out, int out_dt, int64_t M,
+                   int64_t N, int64_t K, int64_t block_size, int gate_up, void* workspace, size_t workspace_bytes,
+                   cudaStream_t st) {
+  if (!limb_tc_supported(wbits, M, N, K, block_size, x, x_dt, w, false))
+    return fail(QMM_ERR_UNSUPPORTED,
+                "split-activation tensor-core kernel: needs an sm_100 device, 1 <= M <= 64, K >= 128 and a multiple of %d, "
+                "block_size 128 or a multiple of 256, 16-byte aligned x/w, no zero point (M=%lld N=%lld K=%lld bs=%lld)",
+                wbits == 8 ? 16 : 32, (long long)M, (long long)N, (long long)K, (long long)block_size);
+  if (gate_up && N % 16 != 0)
+    return fail(QMM_ERR_BAD_SHAPE, "fused gate/up epilogue: the interleaved weight needs a multiple of 16 rows, got %lld", (long long)N);
+  const size_t need = limb_tc_workspace_bytes(M, K);
+  if (!workspace || workspace_bytes < need)
+    return fail(QMM_ERR_WORKSPACE, "split-activation tensor-core kernel needs %zu bytes of workspace, got %zu", need, workspace_bytes);
+  if (!aligned(workspace, 256)) return fail(QMM_ERR_MISALIGNED, "workspace must be 256-byte aligned");
+  const Scratch sc = carve(workspace, M, K, kLimbMaxCtas);
+  const int ncols = ncols_for(M);
+
+  Params p;
+  p.scale = scale;
+  p.pw = sc.pw;
+  p.out = out;
+  p.out_dt = out_dt;
+  p.M = (int)M;
+  p.N = N;
+  p.tiles = (int)ceil_div(N, BMW);
+  p.slots = (int)ceil_div(K, kSlotK);
+  p.mode = block_size <= 0 ? kPerChannel : (block_size == kTileK ? kBlock128 : kBlockSlots);
+  p.S = block_size > 0 ? (int)(K / block_size) : 1;
+  p.spu = p.mode == kBlockSlots ? (int)(block_size / kSlotK) : 1;
+  p.ut = (int)ceil_div(p.slots, p.spu);
+  p.units = (long long)p.tiles * p.ut;
+  p.partial = sc.partial;
+  p.flags = sc.flags;
+  p.err_word = device_error_word();
+  p.gate_up = gate_up;
+  // every CTA should stream at least a few slots, or the fixed cost of a CTA (set-up, partial exchange) dominates
+  const long long min_units = std::max<long long>(1, 2 / p.spu);
+  int grid = (int)std::min<long long>(std::min(sm_count(), kLimbMaxCtas), std::max<long long>(1, p.units / min_units));
+
+  CUtensorMap map_w, map_x;
+  int rc = encode_tmap_2d(&map_w, w, 1, false, (uint64_t)N, (uint64_t)(K * wbits / 8), BMW, 128);
+  if (rc != QMM_OK) return rc;
+  rc = encode_tmap_2d(&map_x, sc.limbs, 1, false, (uint64_t)(3 * M), (uint64_t)K, (uint32_t)ncols, 128);
+  if (rc != QMM_OK) return rc;
+
+  const float pw_mul = wbits == 4 ? 0.0625f : 1.f;
+  cudaError_t e;
+  static const int skip_split = getenv("QMM_EXP_SKIP_SPLIT") ? atoi(getenv("QMM_EXP_SKIP_SPLIT")) : 0;
+  if (skip_split == 2) {  // split only
+    if (x_dt == QMM_BF16) e = launch_split<__nv_bfloat16>(x, sc.limbs, sc.pw, M, K, wbits == 4, pw_mul, st);
+    return QMM_OK;
+  }
+  if (skip_split == 1) {
+    if (wbits == 4) return launch_ncols<4>(ncols, map_w, map_x, p, grid, st);
+    return launch_ncols<8>(ncols, map_w, map_x, p, grid, st);
+  }
+  if (x_dt == QMM_F32) e = launch_split<float>(x, sc.limbs, sc.pw, M, K, wbits == 4, pw_mul, st);
+  else if (x_dt == QMM_BF16) e = launch_split<__nv_bfloat16>(x, sc.limbs, sc.pw, M, K, wbits == 4, pw_mul, st);
+  else e = launch_split<__half>(x, sc.limbs, sc.pw, M, K, wbits == 4, pw_mul, st);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(QMM_ERR_LAUNCH, "split_rows_kernel launch: %s", cudaGetErrorString(e));
+  }
+  int rcl = wbits == 4 ? launch_ncols<4>(ncols, map_w, map_x, p, grid, st) : launch_ncols<8>(ncols, map_w, map_x, p, grid, st);
+  return rcl;
+}
+
+}  // namespace qmm
+
+#ifdef QMM_LIMB_DBG
+extern "C" __attribute__((visibility("default"))) void qmm_debug_limb_dump() {
+  cudaDeviceSynchronize();
+  long long h[64];
+  cudaMemcpyFromSymbol(h, qmm::g_limb_dbg, sizeof(h));
+  const char* names[5] = {"wprod", "bprod", "mma", "drain", "conv"};
+  for (int r = 0; r < 5; ++r)
+    fprintf(stderr, "[dbg] %-6s w0=%lld w1=%lld w2=%lld w3=%lld total=%lld\n", names[r], h[8 * r], h[8 * r + 1], h[8 * r + 2],
+            h[8 * r + 3], h[8 * r + 4]);
+  fprintf(stderr, "[dbg] kernel  cycles=%lld ns=%lld -> %.3f GHz\n", h[40], h[41], h[41] ? (double)h[40] / (double)h[41] : 0.0);
+}
+#endif

@@ -11,8 +11,8 @@
 //      (so every rank computes bit-identical sums), convert and store locally.
 // Two data slots alternate between calls: a rank may start writing call e+1's partial while a slow peer still
 // reads call e's, and passing the barrier of call e+1 proves that every peer has finished call e.
-// No multicast, no TMA, no unbounded spin: a wait that exceeds its budget records an error and the kernel
-// returns without reducing.
+// No multicast, no TMA, no unbounded spin: a wait that exceeds its budget (about a second by default,
+// qmm_set_peer_wait_limit) records an error, fills the result with NaN and returns.
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -24,7 +24,6 @@ namespace qmm {
 namespace {
 
 constexpr int kMaxRanks = 8;
-constexpr long long kPeerWaitCycles = 2000000000ll;  // about a second of SM clock
 
 struct PeerPtrs {
   const float* data[kMaxRanks];  // slot base of every rank's partial (index = rank)
@@ -49,7 +48,7 @@ __device__ __forceinline__ float4 ld_peer_f4(const float* p) {
 
 __global__ void __launch_bounds__(256)
     peer_allreduce_kernel(PeerPtrs pp, int rank, int world, uint32_t epoch_arg, void* __restrict__ out, int out_dt,
-                          int64_t count, uint32_t* err_word) {
+                          int64_t count, uint32_t* err_word, long long wait_cycles) {
   __shared__ int s_ok;
   __shared__ uint32_t s_epoch;
   // epoch_arg == 0: the call number lives in device memory (word 8 of my flag array), so that a captured
@@ -72,7 +71,7 @@ __global__ void __launch_bounds__(256)
     for (int r = 0; r < world && ok; ++r) {
       uint32_t spins = 0;
       while ((int32_t)(ld_acquire_sys(pp.flags[rank] + r) - epoch) < 0) {
-        if ((++spins & 0x3ff) == 0 && clock64() - t0 > kPeerWaitCycles) {
+        if ((++spins & 0x3ff) == 0 && clock64() - t0 > wait_cycles) {
           ok = 0;
           if (err_word) atomicCAS(err_word, 0u, 7u | ((uint32_t)r << 8));
           break;
@@ -89,9 +88,16 @@ __global__ void __launch_bounds__(256)
       *reinterpret_cast<volatile uint32_t*>(my_ctr) = epoch;
     }
   }
-  if (!s_ok) return;
-  // 3. reduce my copy of the whole result (every rank needs all of it: the next layer is replicated)
   const int64_t nvec = count >> 2;
+  if (!s_ok) {
+    // a peer never arrived: the device error word says so; the result is filled with NaN so that a caller who does
+    // not look at the word cannot mistake stale memory for a sum
+    const float nan = __uint_as_float(0x7fc00000u);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x)
+      store_from_f32(out, i, out_dt, nan);
+    return;
+  }
+  // 3. reduce my copy of the whole result (every rank needs all of it: the next layer is replicated)
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int r = 0; r < world; ++r) {
@@ -126,7 +132,7 @@ int launch_peer_allreduce(void* const* data_ptrs, void* const* flag_ptrs, int ra
   const int64_t nvec = count / 4;
   int blocks = (int)std::min<int64_t>(ceil_div(nvec, 256), 2 * sm_count());
   if (blocks < 1) blocks = 1;
-  peer_allreduce_kernel<<<blocks, 256, 0, st>>>(pp, rank, world, epoch, out, out_dt, count, device_error_word());
+  peer_allreduce_kernel<<<blocks, 256, 0, st>>>(pp, rank, world, epoch, out, out_dt, count, device_error_word(), peer_wait_cycles());
   return check_launch("peer_allreduce_kernel");
 }
 

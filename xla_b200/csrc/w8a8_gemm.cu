@@ -48,6 +48,8 @@ struct Params {
   int64_t M, N, K;
   int tiles_m, tiles_n, k_blocks;
   int tma_store;  // 16-bit output staged in shared memory and written with TMA
+  int out_vec;    // `out` rows may be written with 16-byte stores (base and row pitch 16-byte aligned)
+  int acc_vec;    // the same for `acc_out`
   uint32_t* err_word;
 };
 
@@ -251,7 +253,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int ncols = live ? (int)((p.N - n0 < 32) ? (p.N - n0) : 32) : 0;
         if (live && p.acc_out) {
           int32_t* dst = p.acc_out + m * p.N + n0;
-          if (ncols == 32 && (p.N % 4) == 0) {
+          if (ncols == 32 && p.acc_vec) {
 #pragma unroll
             for (int i = 0; i < 8; ++i)
               reinterpret_cast<uint4*>(dst)[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
@@ -267,12 +269,12 @@ __global__ void __launch_bounds__(kThreads, 1)
             v[j] = w8a8_dequant((int32_t)r[j], __ldg(p.w_scale + n), p.zp ? p.zp + n : nullptr, rs, xs);
           }
           if (p.out_dt == QMM_F32)
-            store_row_chunk<float>(reinterpret_cast<float*>(p.out) + m * p.N + n0, v, ncols, (p.N % 4) == 0);
+            store_row_chunk<float>(reinterpret_cast<float*>(p.out) + m * p.N + n0, v, ncols, p.out_vec != 0);
           else if (p.out_dt == QMM_BF16)
             store_row_chunk<__nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(p.out) + m * p.N + n0, v, ncols,
-                                           (p.N % 8) == 0);
+                                           p.out_vec != 0);
           else
-            store_row_chunk<__half>(reinterpret_cast<__half*>(p.out) + m * p.N + n0, v, ncols, (p.N % 8) == 0);
+            store_row_chunk<__half>(reinterpret_cast<__half*>(p.out) + m * p.N + n0, v, ncols, p.out_vec != 0);
         }
       }
       ptx::tcgen05_fence_before();
@@ -309,7 +311,6 @@ int launch_w8a8_tc(const int8_t* xq, const int8_t* w, const float* w_scale, cons
                 "w8a8 tcgen05 kernel: needs an sm_100 device, K a multiple of 16 and 16-byte aligned "
                 "operands (M=%lld N=%lld K=%lld)",
                 (long long)M, (long long)N, (long long)K);
-  if (out && out_dt != QMM_F32 && !aligned(out, 16)) return fail(QMM_ERR_MISALIGNED, "out must be 16-byte aligned");
   CUtensorMap map_x, map_w;
   int rc = encode_tmap_2d(&map_x, xq, 1, false, (uint64_t)M, (uint64_t)K, BM, BK);
   if (rc != QMM_OK) return rc;
@@ -336,6 +337,9 @@ int launch_w8a8_tc(const int8_t* xq, const int8_t* w, const float* w_scale, cons
   }
   Params p;
   p.tma_store = tma_store ? 1 : 0;
+  // vector stores only where every row start is 16-byte aligned; anything else takes the scalar path
+  p.out_vec = (out && aligned(out, 16) && (N * (int64_t)dtype_size(out_dt)) % 16 == 0) ? 1 : 0;
+  p.acc_vec = (acc_out && aligned(acc_out, 16) && N % 4 == 0) ? 1 : 0;
   p.w_scale = w_scale;
   p.zp = zp;
   p.x_scale = x_scale;

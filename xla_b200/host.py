@@ -10,6 +10,9 @@ enqueues one call instead of six.
   lin = pipe.linear(w_packed, scale, block_size=128, weight_is_packed=True)   # weights stay on the device
   lin(x_host, out_host)          # enqueue; returns at once
   pipe.synchronize()             # out_host now holds x_host @ W^T
+
+``linear()`` orders the pipeline after whatever torch's current stream holds at that moment (so a weight packed
+just before is complete when the first linear reads it); ``x_host`` must not be modified until ``synchronize()``.
 """
 import ctypes
 
@@ -81,6 +84,10 @@ class HostPipeline:
     else:
       assert w.dtype == torch.int8
       layout = LAYOUT_W8_BLOCKWISE_KMINOR if blockwise else LAYOUT_W8_PERCHANNEL
+    # the weight may still be in the making on torch's current stream (a pack kernel, an upload): the pipeline's
+    # kernel stream is private and non-blocking, so it is ordered after that work here, once per binding
+    _capi.on_device(self.device, lambda: _capi.check(
+        _capi.lib().qmm_host_pipeline_wait_stream(self._handle, _capi.stream_ptr(self.device))))
     return HostLinear(self, layout, w, scale, zero_point, N, K, block_size if blockwise else 0, _capi.VARIANTS[variant])
 
   def synchronize(self):

@@ -70,7 +70,7 @@ def quantized_gate_up(x, w, scaler, block_size=-1, int4_weight=False, weight_is_
   s32 = _qm._f32(scaler)
   wbits = 4 if weight_is_packed else 8
   fused = (1 <= M <= 32 and x2.dtype in (torch.bfloat16, torch.float16) and K % (512 // wbits) == 0 and
-           (block_size == -1 or block_size % (512 // wbits) == 0) and _qm._variant in ("auto", "mma"))
+           (block_size == -1 or block_size % (512 // wbits) == 0) and _qm.current_variant() in ("auto", "mma"))
   if fused:
     expect = (N2,) if block_size == -1 else (K // block_size, N2)
     assert tuple(s32.shape) == expect, f"weight scaler shape is expect to be {list(expect)}, got {list(s32.shape)}."

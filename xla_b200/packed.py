@@ -107,7 +107,7 @@ def quantized_matmul_packed(x, w, scaler, zero_point=None, block_size=-1, int4_w
   w = w if w.is_contiguous() else w.contiguous()
   s32, zp32 = _qm._f32(scaler), _qm._f32(zero_point)
   L = _capi.lib()
-  variant = _capi.VARIANTS[_qm._variant]
+  variant = _capi.VARIANTS[_qm.current_variant()]
   zp_after = not quantize_activation and _qm._zero_point_outside(M, x2, zero_point)
   out_buf = None if quantize_activation else out
 
@@ -123,18 +123,10 @@ def quantized_matmul_packed(x, w, scaler, zero_point=None, block_size=-1, int4_w
     else:
       out = torch.empty((M, N), dtype=kdt, device=x.device)
     st = _capi.stream_ptr(x.device)
-    args = (x2.data_ptr(), _capi.dtype_code(x2.dtype), w.data_ptr(), s32.data_ptr(),
-            None if zp_after else _capi.ptr(zp32), out.data_ptr(), _capi.dtype_code(kdt), M, N, K)
-    if weight_is_packed:
-      if block_size == -1:
-        _capi.check(L.qmm_w4a16_perchannel_packed(*args, variant, st))
-      else:
-        _capi.check(L.qmm_w4a16_blockwise_packed(*args, block_size, variant, st))
-    else:
-      if block_size == -1:
-        _capi.check(L.qmm_w8a16_perchannel(*args, variant, st))
-      else:
-        _capi.check(L.qmm_w8a16_blockwise(*args, block_size, variant, st))
+    ws, ws_bytes = _capi.workspace(x.device, M, K) if M <= 64 else (None, 0)
+    _capi.check(L.qmm_weight_only(4 if weight_is_packed else 8, x2.data_ptr(), _capi.dtype_code(x2.dtype), w.data_ptr(),
+                                  s32.data_ptr(), None if zp_after else _capi.ptr(zp32), out.data_ptr(), _capi.dtype_code(kdt),
+                                  M, N, K, 0 if block_size == -1 else block_size, variant, ws, ws_bytes, st))
     if zp_after:
       out = _qm._subtract_zero_point(out, x2, zp32, block_size).to(out_dtype)
       if out_buf is not None:

@@ -30,33 +30,40 @@ XLA_LIB = torch.library.Library("xla", "FRAGMENT")
 if not has_xla_op("quantized_matmul"):
   XLA_LIB.define(SCHEMA)
 
-# Kernel family forced for the calls made inside a `force_variant` block ("auto" otherwise).
-_variant = "auto"
-# How the activation quantizer converts a pre-cast +128: saturate to 127 (what an XLA device does)
-# or wrap to -128 (what the reference's eager CPU kernel does).
-_saturate = True
+# Per-thread settings: the kernel family forced inside a `force_variant` block ("auto" otherwise) and how the
+# activation quantizer converts a pre-cast +128 - saturate to 127 (what an XLA device does, the default) or wrap to
+# -128 (what the reference's eager CPU kernel does).  Thread-local, so that concurrent callers do not see each other's.
+import threading
+
+_tls = threading.local()
+
+
+def current_variant():
+  return getattr(_tls, "variant", "auto")
+
+
+def current_saturation():
+  return getattr(_tls, "saturate", True)
 
 
 class force_variant:
-  """Context manager: run the ops with one kernel family ("generic", "gemv", "tcgen05", "auto")."""
+  """Context manager: run this thread's ops with one kernel family ("generic", "gemv", "tcgen05", "mma", "i8tc", "auto")."""
 
   def __init__(self, name):
     assert name in _capi.VARIANTS, name
     self.name = name
 
   def __enter__(self):
-    global _variant
-    self.prev, _variant = _variant, self.name
+    self.prev = current_variant()
+    _tls.variant = self.name
 
   def __exit__(self, *exc):
-    global _variant
-    _variant = self.prev
+    _tls.variant = self.prev
 
 
 def set_activation_saturation(saturate: bool):
-  """True (default): int8 conversion clamps; False: wraps +128 to -128 like eager CPU."""
-  global _saturate
-  _saturate = bool(saturate)
+  """True (default): int8 conversion clamps; False: wraps +128 to -128 like eager CPU.  Applies to the calling thread."""
+  _tls.saturate = bool(saturate)
 
 
 # ---- shape checks ---------------------------------------------------------------------------------
@@ -85,8 +92,10 @@ def _check_per_channel_quant_weight_dtype_shapes(input_dim, output_dim, w, w_sca
       w_scaler.dim() == 1 and w_scaler.shape[0] == dims[0],
       f"weight scaler shape is expect to be [out_channel,], got {w_scaler.shape}, weight shape {dims}.")
   if zero_point is not None:
+    # (the reference tests the scaler's length here a second time; the kernels index zero_point[n] for every n,
+    # so its own length is what has to match)
     _expect(
-        zero_point.dim() == 1 and w_scaler.shape[0] == dims[0],
+        zero_point.dim() == 1 and zero_point.shape[0] == dims[0],
         f"zero point shape is expect to be [out_channel,], got {zero_point.shape}, weight shape {dims}.")
 
 
@@ -133,7 +142,7 @@ def _zero_point_outside(M, x2, zero_point):
   """True when the zero-point term is applied after the kernel: the tensor-core and register-dequant
   kernels take symmetric weights only, and the any-shape kernel that does take a zero point is far slower
   than one of them plus a rank-S update (S = number of scale blocks)."""
-  return (zero_point is not None and M > 8 and _variant == "auto" and
+  return (zero_point is not None and M > 8 and current_variant() == "auto" and
           x2.dtype in (torch.bfloat16, torch.float16))
 
 
@@ -163,7 +172,7 @@ def quantize_tensor(x, saturate=None):
   M, K = x2.shape
   xq = torch.empty((M, K), dtype=torch.int8, device=x.device)
   xs = torch.empty((M,), dtype=torch.float32, device=x.device)
-  sat = _saturate if saturate is None else saturate
+  sat = current_saturation() if saturate is None else saturate
   with torch.cuda.device(x.device):
     _capi.check(_capi.lib().qmm_quantize_activation(
         _capi.ptr(x2), _capi.dtype_code(x2.dtype), _capi.ptr(xq), _capi.ptr(xs), None, M, K, int(sat),
@@ -182,9 +191,45 @@ def _w8a8(x2, w, scaler, zero_point, out_dtype):
   ws = torch.empty((nbytes,), dtype=torch.uint8, device=x2.device)
   _capi.check(L.qmm_w8a8_perchannel(
       _capi.ptr(x2), _capi.dtype_code(x2.dtype), _capi.ptr(w), _capi.ptr(scaler), _capi.ptr(zero_point),
-      _capi.ptr(out), _capi.dtype_code(out_dtype), M, N, K, int(_saturate), _capi.VARIANTS[_variant],
+      _capi.ptr(out), _capi.dtype_code(out_dtype), M, N, K, int(current_saturation()), _capi.VARIANTS[current_variant()],
       _capi.ptr(ws), nbytes, _capi.stream_ptr(x2.device)))
   return out
+
+
+# K-minor copies of blockwise weights that arrive in the reference layout [in/block, block, out] (N minor), keyed by
+# the weight tensor object: id -> (weak reference, version counter, storage address, converted weight, is_packed).
+# An entry dies with its tensor (weak-reference callback) and is rebuilt when the tensor was written in place.
+_kminor_cache = {}
+_kminor_enabled = True
+
+
+def set_prepack_cache(enabled: bool):
+  """Turns the operator's K-minor weight cache on or off (off: every blockwise call on the reference layout runs
+  the any-shape kernel) and drops what it holds."""
+  global _kminor_enabled
+  _kminor_enabled = bool(enabled)
+  _kminor_cache.clear()
+
+
+def _kminor_weight(w, int4_weight):
+  """[S, bs, N] int8 -> (packed int4 [N, K/2], True) or (int8 [N, K], False), converted once per weight tensor."""
+  import weakref
+  key = id(w)
+  hit = _kminor_cache.get(key)
+  if hit is not None and hit[0]() is w and hit[1] == w._version and hit[2] == w.data_ptr():
+    return hit[3], hit[4]
+  K = w.shape[0] * w.shape[1]
+  if int4_weight and K % 2 == 0:
+    from . import packed
+    conv, is_packed = packed.pack_int4(w, layout="sbn"), True
+  else:
+    conv, is_packed = w.reshape(K, -1).t().contiguous(), False
+  try:
+    ref = weakref.ref(w, lambda _r, k=key: _kminor_cache.pop(k, None))
+  except TypeError:
+    return conv, is_packed  # not weak-referenceable: convert every time rather than risk a stale entry
+  _kminor_cache[key] = (ref, w._version, w.data_ptr(), conv, is_packed)
+  return conv, is_packed
 
 
 def quantized_matmul_cuda(x, w, scaler, zero_point=None, block_size=-1, int4_weight=False,
@@ -203,6 +248,14 @@ def quantized_matmul_cuda(x, w, scaler, zero_point=None, block_size=-1, int4_wei
     _check_blockwise_quant_weight_dtype_shapes(K, w.shape[-1], block_size, w, scaler, zero_point)
     N = w.shape[-1]
   out_dtype = _out_dtype(x, scaler, zero_point)
+  if (block_size != -1 and _kminor_enabled and current_variant() == "auto" and w.is_contiguous() and
+      (id(w) in _kminor_cache or not torch.cuda.is_current_stream_capturing())):
+    # The streaming kernels read K-minor rows; the reference layout is N minor.  The weight is converted once (a
+    # device-side transpose / int4 pack, cached per weight tensor) and the call continues on the packed operator.
+    from . import packed
+    wk, is_packed = _kminor_weight(w, bool(int4_weight))
+    return packed.quantized_matmul_packed(x, wk, scaler, zero_point, block_size=block_size, int4_weight=bool(int4_weight),
+                                          weight_is_packed=is_packed, out_dtype=out_dtype)
   x2 = _rows(x)
   M = x2.shape[0]
   w = w if w.is_contiguous() else w.contiguous()
@@ -219,9 +272,10 @@ def quantized_matmul_cuda(x, w, scaler, zero_point=None, block_size=-1, int4_wei
     args = (x2.data_ptr(), _capi.dtype_code(x2.dtype), w.data_ptr(), scaler32.data_ptr(),
             None if zp_after else _capi.ptr(zp32), out.data_ptr(), _capi.dtype_code(kdt), M, N, K)
     if block_size == -1:
-      _capi.check(L.qmm_w8a16_perchannel(*args, _capi.VARIANTS[_variant], _capi.stream_ptr(x.device)))
+      ws, ws_bytes = _capi.workspace(x.device, M, K) if M <= 64 else (None, 0)
+      _capi.check(L.qmm_weight_only(8, *args, 0, _capi.VARIANTS[current_variant()], ws, ws_bytes, _capi.stream_ptr(x.device)))
     else:
-      _capi.check(L.qmm_blockwise_sbn(*args, block_size, _capi.VARIANTS[_variant], _capi.stream_ptr(x.device)))
+      _capi.check(L.qmm_blockwise_sbn(*args, block_size, _capi.VARIANTS[current_variant()], _capi.stream_ptr(x.device)))
     if zp_after:
       out = _subtract_zero_point(out, x2, zp32, -1).to(out_dtype)
     return out
