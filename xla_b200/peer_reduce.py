@@ -75,10 +75,20 @@ class FusedRowParallelDecode:
         self.rank, self.world, self.max_M * self.N, _capi.stream_ptr(self.device)))
     return out.reshape(x_local.shape[:-1] + (self.N,))
 
+  def check(self):
+    """Raises TimeoutError if a kernel on this device gave up waiting for a peer's tile since the last check (the
+    affected outputs are NaN).  Synchronises the current stream; call it wherever a step's results are consumed."""
+    _capi.check_device(self.device)
+
   def close(self):
     if self._own is None:
       return
     torch.cuda.synchronize(self.device)
+    word = _capi.device_error(self.device)
+    if word:
+      import warnings
+      warnings.warn(f"xla_b200: a peer exchange on {self.device} gave up a wait (code {word & 0xff}, rank {word >> 8}); "
+                    "results of that call were NaN")
     dist.barrier(group=self.group)
     L = _capi.lib()
     for r, p in enumerate(self._ptrs):
@@ -149,11 +159,21 @@ class PeerAllReduce:
                                                   _capi.stream_ptr(self.device)))
     return out
 
+  def check(self):
+    """Raises TimeoutError if an exchange on this device gave up waiting for a peer since the last check (the
+    affected result is NaN).  Synchronises the current stream; call it wherever a step's results are consumed."""
+    _capi.check_device(self.device)
+
   def close(self):
     """Unmaps the peers' buffers and frees this rank's (collective: every rank must call it)."""
     if self._own is None:
       return
     torch.cuda.synchronize(self.device)
+    word = _capi.device_error(self.device)
+    if word:
+      import warnings
+      warnings.warn(f"xla_b200: a peer exchange on {self.device} gave up a wait (code {word & 0xff}, rank {word >> 8}); "
+                    "results of that call were NaN")
     dist.barrier(group=self.group)
     L = _capi.lib()
     for r, p in enumerate(self._ptrs):
