@@ -60,7 +60,7 @@ typedef enum qmm_variant {
   QMM_VARIANT_GEMV = 2,    /* decode: warp-per-row, 128-bit weight loads, M <= 8 */
   QMM_VARIANT_TCGEN05 = 3, /* TMA -> shared memory -> tcgen05.mma with TMEM accumulators */
   QMM_VARIANT_MMA = 4,     /* decode: weights dequantised in registers into warp-level MMAs, M <= 32 */
-  QMM_VARIANT_TMEM = 5,    /* decode: weights dequantised in registers into tensor memory, tcgen05.mma, M <= 32 */
+  /* 5 was a tensor-memory decode variant that lost to QMM_VARIANT_MMA on every shape; the value is not reused */
   QMM_VARIANT_I8TC = 6,    /* activations split into int8 limbs, unconverted weights into tcgen05.mma.kind::i8, stream-K
                               over all SMs, 1 <= M <= 64; only through qmm_weight_only (needs workspace) */
 } qmm_variant;
@@ -152,6 +152,14 @@ QMM_API int qmm_w8a16_blockwise(const void* x, int x_dtype, const int8_t* w, con
  *   (torch_xla/experimental/xla_quantized_matmul.py:101-124 XLA key, :152-170 CPU key).
  */
 QMM_API size_t qmm_weight_only_workspace_size(int64_t max_M, int64_t K);
+/*
+ * The kernel family the measured table names for a shape (a QMM_VARIANT_* value), or 0 when the table has no entry
+ * and QMM_VARIANT_AUTO falls back to its shape rule.  The table is generated on a B200 by `python -m xla_b200.tune`
+ * and compiled in; it is keyed by weight bits, block size (<= 0: per channel), out/in features and the batch
+ * bucket M <= 1, 2, 4, 8, 16, 32, 64.
+ * Replaces: get_tuned_block_sizes (torch_xla/experimental/pallas_kernels/quantized_matmul_kernel.py:537-555).
+ */
+QMM_API int qmm_tuned_variant(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size);
 QMM_API int qmm_weight_only(int wbits, const void* x, int x_dtype, const void* w, const float* scale, const float* zp,
                     void* out, int out_dtype, int64_t M, int64_t N, int64_t K, int64_t block_size, int variant,
                     void* workspace, size_t workspace_bytes, void* stream);
@@ -353,14 +361,6 @@ QMM_API int qmm_device_error_flag(uint32_t* flag, void* stream);
  * runtime (torch_xla/csrc/runtime/), not in this operator.
  */
 QMM_API int qmm_set_peer_wait_limit(double seconds);
-
-/*
- * Pipeline tracing for the tensor-core weight-only kernel: while a device buffer of 4 x 1024 int64 is
- * registered, CTA (0,0) of every launch logs SM-clock timestamps of its pipeline events into it
- * (row 0 dequant warp, row 1 MMA issuer, row 2 drain warp, row 3 weight producer).  NULL turns it off.
- * Stands in for the reference's TraceMe/xprof hooks on this path (torch_xla/debug/profiler.py:106-181).
- */
-QMM_API int qmm_debug_set_trace(void* device_buffer);
 
 /* Name of the kernel family the AUTO heuristic picks (static string, for logs and tests). */
 QMM_API const char* qmm_variant_for(int op, int64_t M, int64_t N, int64_t K, int64_t block_size,

@@ -505,58 +505,6 @@ def test_mma_staged_tile_slots_and_rounds(N):
 # ---------------------------------------------------------------------------------------------
 
 
-@pytest.mark.parametrize("xdtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("M,bs", [(1, 128), (8, 128), (9, 256), (16, 64), (17, 128), (32, 128), (4, -1), (24, -1)])
-def test_tmem_w4a16_packed(M, bs, xdtype):
-  g = qc.gen(30)
-  N, K = 1000, 2304  # N not a multiple of 128; K = 36 k tiles: splits over 4 CTAs at most
-  x = qc.activations(g, M, K, dtype=xdtype)
-  w_nk = qc.int4_weight(g, N, K)
-  wp = xla_b200.pack_int4(cu(w_nk))
-  if bs == -1:
-    s = qc.per_channel_scale(g, N)
-    exact = qo.quantized_matmul(x, w_nk, s, dot_round=None)
-  else:
-    s = qc.blockwise_scale(g, K // bs, N)
-    exact = qo.quantized_matmul(x.float(), qc.to_sbn(w_nk, bs), s, block_size=bs, dot_round=None)
-  out = packed_op(cu(x), wp, cu(s), block_size=bs, int4_weight=True, weight_is_packed=True, variant="tmem")
-  assert out.dtype == torch.float32 and out.shape == (M, N)
-  assert qo.max_abs_rel(out, exact) < TOL_F32
-
-
-@pytest.mark.parametrize("xdtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("M", [1, 13, 32])
-def test_tmem_w8a16_per_channel(M, xdtype):
-  g = qc.gen(31)
-  N, K = 1000, 2112  # 33 k tiles: no split
-  x = qc.activations(g, M, K, dtype=xdtype)
-  w = qc.int8_weight(g, N, K)
-  s = qc.per_channel_scale(g, N)
-  out = op(cu(x), cu(w), cu(s), variant="tmem")
-  assert qo.max_abs_rel(out, qo.quantized_matmul(x, w, s, dot_round=None)) < TOL_F32
-  with pytest.raises(NotImplementedError):
-    op(cu(qc.activations(g, 33, K, dtype=xdtype)), cu(w), cu(s), variant="tmem")
-
-
-@pytest.mark.parametrize("N", [128 * 40 + 7, 128 * 200])
-def test_tmem_rounds_and_passes(N):
-  """More row blocks than clusters (several rounds per cluster) and, for the larger N, more rounds than the
-  shared-memory partial buffer holds (several passes)."""
-  g = qc.gen(32)
-  K, bs, M = 1024, 128, 20
-  x = qc.activations(g, M, K)
-  w_nk = qc.int4_weight(g, N, K)
-  wp = xla_b200.pack_int4(cu(w_nk))
-  s = qc.blockwise_scale(g, K // bs, N)
-  exact = qo.quantized_matmul(x.float(), qc.to_sbn(w_nk, bs), s, block_size=bs, dot_round=None)
-  out = packed_op(cu(x), wp, cu(s), block_size=bs, int4_weight=True, weight_is_packed=True, variant="tmem")
-  assert qo.max_abs_rel(out, exact) < TOL_F32
-  f = ctypes.c_uint32(7)
-  with torch.cuda.device(0):
-    assert _capi.lib().qmm_device_error_flag(ctypes.byref(f), _capi.stream_ptr()) == 0
-  assert f.value == 0
-
-
 # ---------------------------------------------------------------------------------------------
 # int8 blockwise weights stored K-minor (what the module keeps for the fast kernels)
 # ---------------------------------------------------------------------------------------------

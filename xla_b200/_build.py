@@ -8,7 +8,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libqmm_b200.so")
-SOURCES = ["abi.cu", "generic.cu", "gemv.cu", "act_quant.cu", "pack.cu", "w8a8_gemm.cu", "mixed_gemm.cu", "limb_gemm.cu", "decode_mma.cu", "decode_tc.cu",
+SOURCES = ["abi.cu", "generic.cu", "gemv.cu", "act_quant.cu", "pack.cu", "w8a8_gemm.cu", "mixed_gemm.cu", "limb_gemm.cu", "decode_mma.cu",
            "static_scratch.cu", "peer_reduce.cu", "host_pipeline.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math=false",
@@ -35,7 +35,7 @@ def build(force=False, verbose=False):
   os.makedirs(LIB_DIR, exist_ok=True)
   obj_dir = os.path.join(LIB_DIR, "obj")
   os.makedirs(obj_dir, exist_ok=True)
-  headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
+  headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h", ".inc"))]
   headers.append(os.path.join(os.path.dirname(HERE), "include", "qmm_b200.h"))
   nvcc = _nvcc()
   objs, procs = [], []

@@ -11,10 +11,10 @@ import torch
 from . import _build
 
 F32, BF16, F16 = 0, 1, 2
-AUTO, GENERIC, GEMV, TCGEN05, MMA, TMEM, I8TC = 0, 1, 2, 3, 4, 5, 6
+AUTO, GENERIC, GEMV, TCGEN05, MMA, I8TC = 0, 1, 2, 3, 4, 6
 OP_W8A16_PERCHANNEL, OP_BLOCKWISE_SBN, OP_W4A16_BLOCKWISE_PACKED, OP_W8A8_PERCHANNEL, OP_W4A16_PERCHANNEL_PACKED = range(5)
 
-VARIANTS = {"auto": AUTO, "generic": GENERIC, "gemv": GEMV, "tcgen05": TCGEN05, "mma": MMA, "tmem": TMEM, "i8tc": I8TC}
+VARIANTS = {"auto": AUTO, "generic": GENERIC, "gemv": GEMV, "tcgen05": TCGEN05, "mma": MMA, "i8tc": I8TC}
 
 _DTYPES = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
 
@@ -30,6 +30,7 @@ SIGNATURES = {
     "qmm_w4a16_perchannel_packed": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i, _p]),
     "qmm_w8a16_blockwise": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _p]),
     "qmm_weight_only_workspace_size": (_sz, [_i64, _i64]),
+    "qmm_tuned_variant": (_i, [_i, _i64, _i64, _i64, _i64]),
     "qmm_weight_only": (_i, [_i, _p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _p, _sz, _p]),
     "qmm_host_pipeline_create": (_i, [_sz, _sz, _i, ctypes.POINTER(ctypes.c_void_p)]),
     "qmm_host_weight_only": (_i, [_p, _i, _p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i]),
@@ -58,7 +59,6 @@ SIGNATURES = {
     "qmm_unpack_int4_nk": (_i, [_p, _p, _i64, _i64, _p]),
     "qmm_device_error_flag": (_i, [_p, _p]),
     "qmm_set_peer_wait_limit": (_i, [ctypes.c_double]),
-    "qmm_debug_set_trace": (_i, [_p]),
     "qmm_variant_for": (ctypes.c_char_p, [_i, _i64, _i64, _i64, _i64, _i]),
 }
 

@@ -85,8 +85,6 @@ uint32_t* device_error_word() {
 static std::atomic<long long> g_peer_wait_cycles{2000000000ll};  // about a second of SM clock
 long long peer_wait_cycles() { return g_peer_wait_cycles.load(std::memory_order_relaxed); }
 
-static long long* g_trace = nullptr;
-long long* debug_trace_buffer() { return g_trace; }
 
 // ---- tensor maps --------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -210,10 +208,6 @@ int qmm_w8a16_perchannel(const void* x, int x_dtype, const int8_t* w, const floa
       log_choice("w8a16_perchannel", "mma", M, N, K);
       if (zp) return fail(QMM_ERR_UNSUPPORTED, "the register-dequant decode kernel does not take a zero point");
       return launch_decode_mma(8, x, x_dtype, w, scale, out, out_dtype, M, N, K, 0, st);
-    case QMM_VARIANT_TMEM:
-      log_choice("w8a16_perchannel", "tmem", M, N, K);
-      if (zp) return fail(QMM_ERR_UNSUPPORTED, "w8a16_perchannel: the tensor-memory decode kernel takes no zero point");
-      return launch_decode_tc(8, x, x_dtype, w, scale, out, out_dtype, M, N, K, 0, st);
     case QMM_VARIANT_TCGEN05:
       log_choice("w8a16_perchannel", "tcgen05", M, N, K);
       if (zp) return fail(QMM_ERR_UNSUPPORTED, "tcgen05 weight-only kernel does not take a zero point");
@@ -264,10 +258,6 @@ int qmm_w4a16_blockwise_packed(const void* x, int x_dtype, const uint8_t* wp, co
       log_choice("w4a16_blockwise_packed", "mma", M, N, K);
       if (zp) return fail(QMM_ERR_UNSUPPORTED, "the register-dequant decode kernel does not take a zero point");
       return launch_decode_mma(4, x, x_dtype, wp, scale, out, out_dtype, M, N, K, block_size, st);
-    case QMM_VARIANT_TMEM:
-      log_choice("w4a16_blockwise_packed", "tmem", M, N, K);
-      if (zp) return fail(QMM_ERR_UNSUPPORTED, "w4a16_blockwise_packed: the tensor-memory decode kernel takes no zero point");
-      return launch_decode_tc(4, x, x_dtype, wp, scale, out, out_dtype, M, N, K, block_size, st);
     case QMM_VARIANT_TCGEN05:
       log_choice("w4a16_blockwise_packed", "tcgen05", M, N, K);
       if (zp) return fail(QMM_ERR_UNSUPPORTED, "tcgen05 weight-only kernel does not take a zero point");
@@ -298,10 +288,6 @@ int qmm_w8a16_blockwise(const void* x, int x_dtype, const int8_t* w, const float
       log_choice("w8a16_blockwise", "mma", M, N, K);
       if (zp) return fail(QMM_ERR_UNSUPPORTED, "the register-dequant decode kernel does not take a zero point");
       return launch_decode_mma(8, x, x_dtype, w, scale, out, out_dtype, M, N, K, block_size, st);
-    case QMM_VARIANT_TMEM:
-      log_choice("w8a16_blockwise", "tmem", M, N, K);
-      if (zp) return fail(QMM_ERR_UNSUPPORTED, "w8a16_blockwise: the tensor-memory decode kernel takes no zero point");
-      return launch_decode_tc(8, x, x_dtype, w, scale, out, out_dtype, M, N, K, block_size, st);
     case QMM_VARIANT_TCGEN05:
       log_choice("w8a16_blockwise", "tcgen05", M, N, K);
       if (zp) return fail(QMM_ERR_UNSUPPORTED, "tcgen05 weight-only kernel does not take a zero point");
@@ -309,6 +295,34 @@ int qmm_w8a16_blockwise(const void* x, int x_dtype, const int8_t* w, const float
     default:
       return fail(QMM_ERR_UNSUPPORTED, "unknown variant %d", variant);
   }
+}
+
+// ---- tuned kernel choice ------------------------------------------------------------------------------------------
+// The counterpart of the reference's TUNED_BLOCK_SIZES / get_tuned_block_sizes
+// (torch_xla/experimental/pallas_kernels/quantized_matmul_kernel.py:326-555): measured on a B200 by xla_b200/tune.py.
+namespace {
+struct TunedRow {
+  int wbits, block_size;
+  int64_t N, K;
+  unsigned char choice[7];  // QMM_VARIANT_* for M <= 1, 2, 4, 8, 16, 32, 64; 0 = not measured
+};
+const TunedRow kTuned[] = {
+#include "tuned_table.inc"
+    {0, 0, 0, 0, {0, 0, 0, 0, 0, 0, 0}},  // end
+};
+
+int tuned_variant(int wbits, int64_t block_size, int64_t M, int64_t N, int64_t K) {
+  if (M < 1 || M > 64) return 0;
+  int bucket = 0;
+  while ((1 << bucket) < M) ++bucket;
+  for (const TunedRow* r = kTuned; r->wbits; ++r)
+    if (r->wbits == wbits && r->block_size == block_size && r->N == N && r->K == K) return r->choice[bucket];
+  return 0;
+}
+}  // namespace
+
+int qmm_tuned_variant(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size) {
+  return tuned_variant(wbits, block_size < 0 ? 0 : block_size, M, N, K);
 }
 
 size_t qmm_weight_only_workspace_size(int64_t max_M, int64_t K) {
@@ -329,7 +343,18 @@ int qmm_weight_only(int wbits, const void* x, int x_dtype, const void* w, const 
                   (long long)K, (long long)block_size);
     const bool can = limb_tc_supported(wbits, M, N, K, block_size, x, x_dtype, w, zp != nullptr) && workspace &&
                      workspace_bytes >= limb_tc_workspace_bytes(M, K) && aligned(workspace, 256);
-    if (variant == QMM_VARIANT_I8TC || (can && limb_tc_preferred(wbits, M, N, K, block_size))) {
+    // AUTO: the measured table first, the shape rule where the table has no entry for this shape
+    const int tuned = variant == QMM_VARIANT_AUTO ? tuned_variant(wbits, block_size, M, N, K) : 0;
+    bool use = variant == QMM_VARIANT_I8TC;
+    if (variant == QMM_VARIANT_AUTO && can) use = tuned ? tuned == QMM_VARIANT_I8TC : limb_tc_preferred(wbits, M, N, K, block_size);
+    if (!use && tuned && tuned != QMM_VARIANT_I8TC && !zp) {
+      // the table names one of the kernels behind the entry points below; they refuse what they cannot run, and AUTO
+      // then decides there
+      const bool ok = tuned == QMM_VARIANT_MMA ? decode_mma_supported(wbits, M, N, K, block_size, x, x_dtype, w, false)
+                                               : (tuned == QMM_VARIANT_TCGEN05 && mixed_tc_supported(wbits, M, N, K, block_size, x, x_dtype, w, false));
+      if (ok) variant = tuned;
+    }
+    if (use) {
       log_choice("weight_only", "i8tc", M, N, K);
       if (zp) return fail(QMM_ERR_UNSUPPORTED, "the split-activation tensor-core kernel does not take a zero point");
       return launch_limb_tc(wbits, x, x_dtype, w, scale, out, out_dtype, M, N, K, block_size, 0, workspace, workspace_bytes,
@@ -387,10 +412,6 @@ int qmm_w4a16_perchannel_packed(const void* x, int x_dtype, const uint8_t* wp, c
       log_choice("w4a16_perchannel_packed", "mma", M, N, K);
       if (zp) return fail(QMM_ERR_UNSUPPORTED, "the register-dequant decode kernel does not take a zero point");
       return launch_decode_mma(4, x, x_dtype, wp, scale, out, out_dtype, M, N, K, 0, st);
-    case QMM_VARIANT_TMEM:
-      log_choice("w4a16_perchannel_packed", "tmem", M, N, K);
-      if (zp) return fail(QMM_ERR_UNSUPPORTED, "w4a16_perchannel_packed: the tensor-memory decode kernel takes no zero point");
-      return launch_decode_tc(4, x, x_dtype, wp, scale, out, out_dtype, M, N, K, 0, st);
     case QMM_VARIANT_TCGEN05:
       log_choice("w4a16_perchannel_packed", "tcgen05", M, N, K);
       if (zp) return fail(QMM_ERR_UNSUPPORTED, "tcgen05 weight-only kernel does not take a zero point");
@@ -591,11 +612,6 @@ int qmm_device_error_flag(uint32_t* flag, void* stream) {
 int qmm_set_peer_wait_limit(double seconds) {
   if (!(seconds > 0.0) || seconds > 60.0) return fail(QMM_ERR_BAD_SHAPE, "peer wait limit must be in (0, 60] seconds, got %g", seconds);
   g_peer_wait_cycles.store((long long)(seconds * 2.0e9), std::memory_order_relaxed);  // ~2 GHz SM clock
-  return QMM_OK;
-}
-
-int qmm_debug_set_trace(void* device_buffer) {
-  g_trace = reinterpret_cast<long long*>(device_buffer);
   return QMM_OK;
 }
 

@@ -22,9 +22,6 @@ uint32_t* device_error_word();  // device address of the flag for the current de
 // How long a kernel waits for another GPU before it gives up, in SM clock cycles (qmm_set_peer_wait_limit).
 long long peer_wait_cycles();
 
-// Caller-provided device buffer for pipeline timestamps (nullptr = tracing off).
-long long* debug_trace_buffer();
-
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }

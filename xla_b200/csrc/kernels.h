@@ -53,19 +53,11 @@ int launch_decode_mma_allreduce(int wbits, const void* x, int x_dt, const void* 
                                 int64_t M, int64_t N, int64_t K, int64_t block_size, void* const* peer_bufs, int rank,
                                 int world, int64_t slot_floats, cudaStream_t st);
 
-// ---- decode_tc.cu -------------------------------------------------------------------------
-// Decode kernel on tcgen05 with the weight operand written to tensor memory (M <= 32, bf16/f16
-// activations, no zero point), K split over a thread-block cluster.
-bool decode_tc_supported(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size, const void* x, int x_dt,
-                         const void* w, bool has_zp);
-int launch_decode_tc(int wbits, const void* x, int x_dt, const void* w, const float* scale, void* out, int out_dt,
-                     int64_t M, int64_t N, int64_t K, int64_t block_size, cudaStream_t st);
-
 // ---- limb_gemm.cu (tcgen05 kind::i8 on unconverted weights; activations split into int8 limbs) ----------
 // Weight-only linear for 1 <= M <= 64 (bf16/f16/f32 activations, no zero point): stream-K over all SMs, needs
 // limb_tc_workspace_bytes(M, K) bytes of caller scratch whose first 1024 bytes are zero before the first use (the
 // kernel leaves them zero).  gate_up as in launch_decode_mma.
-constexpr int kLimbMaxCtas = 192;
+constexpr int kLimbMaxCtas = 320;  // two CTAs per SM on up to 160 SMs
 size_t limb_tc_workspace_bytes(int64_t M, int64_t K);
 bool limb_tc_shape_ok(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size, int x_dt, bool has_zp);
 bool limb_tc_supported(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size, const void* x, int x_dt,

@@ -60,10 +60,12 @@ constexpr uint32_t kSmemBudget = 227 * 1024 - 1024 /*alignment*/ - 1024 /*barrie
 #ifdef QMM_LIMB_DBG
 }  // namespace
 __device__ long long g_limb_dbg[64];
+__device__ long long g_limb_cta[4 * 512];  // per CTA: entry, first slot full, MMAs issued, exit (globaltimer ns)
 namespace {
 #define DBG_DECL long long dbg_t = 0, dbg_w[4] = {0, 0, 0, 0}; const long long dbg_t0 = clock64(); (void)dbg_t
 #define DBG_BEGIN() dbg_t = clock64()
 #define DBG_END(i) dbg_w[i] += clock64() - dbg_t
+#define DBG_STAMP(i) if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) g_limb_dbg[42 + (i)] = (long long)ptx::globaltimer_ns()
 #define DBG_FLUSH(base)                                                  \
   if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) {                      \
     for (int i_ = 0; i_ < 4; ++i_) g_limb_dbg[(base) + i_] = dbg_w[i_];  \
@@ -73,6 +75,7 @@ namespace {
 #define DBG_DECL
 #define DBG_BEGIN()
 #define DBG_END(i)
+#define DBG_STAMP(i)
 #define DBG_FLUSH(base)
 #endif
 
@@ -108,25 +111,35 @@ struct Params {
 template <int WBITS, int NCOLS>
 struct Cfg {
   static constexpr uint32_t kBTile = NCOLS * 128;
-  // int4 with up to 96 limb columns: the expanded weight operand lives in tensor memory (64 columns per slot, four
-  // slots in the upper half of TMEM) and never touches shared memory; the ring slots then hold limb tiles only
+  // CTAs per SM.  With int4 weights and up to 48 limb columns a CTA takes at most half of an SM's shared memory, tensor memory and
+  // registers, and two run side by side: whenever one pipeline waits (a hand-over between warps, the partial-tile
+  // exchange at the end of a K range, its own start-up) the other's MMAs keep the tensor pipe and the weight stream
+  // busy, and a kernel's first CTAs overlap the last ones of the kernel before it.
+  static constexpr int kOcc = (WBITS == 4 && NCOLS <= 48) ? 2 : 1;
+  static constexpr int kTmemCols = 512 / kOcc;
+  static constexpr uint32_t kBudget = kOcc == 2 ? 110 * 1024 - 2048 : kSmemBudget;
+  // int4 with up to 96 limb columns: the expanded weight operand lives in tensor memory (64 columns per slot, in the
+  // upper half of the CTA's columns) and never touches shared memory; the ring slots then hold limb tiles only
   static constexpr bool kATmem = WBITS == 4 && NCOLS <= 96;
-  static constexpr int kATmemCol0 = 256, kATmemSlotCols = 64;
+  static constexpr int kATmemCol0 = kTmemCols / 2, kATmemSlotCols = 64;
   static constexpr uint32_t kAInSlot = kATmem ? 0 : kASlot;
   static constexpr uint32_t kSlot = kAInSlot + 2 * kBTile;   // [A tile 0 | A tile 1 |] B tile 0 | B tile 1
-  static constexpr int kSlots = kATmem ? 4 : (WBITS == 4 ? 2 : std::min<int>(6, kSmemBudget / kSlot));
-  static constexpr int kRawFit = WBITS == 4 ? (int)((kSmemBudget - kSlots * kSlot) / kRawBytes) : 0;
-  static constexpr int kRaw = WBITS == 4 ? std::min(10, kRawFit & ~1) : 0;   // even: each group of expanding warps owns alternate slots
-  static constexpr int kAccCols = kATmem ? kATmemCol0 : 512;
+  static constexpr int kSlots = kATmem ? kATmemCol0 / kATmemSlotCols : (WBITS == 4 ? 2 : std::min<int>(6, kBudget / kSlot));
+  // expanding warps: two groups of four that take alternate slots, or one group where two CTAs share the SM
+  static constexpr int kGroups = WBITS == 4 ? (kOcc == 2 ? 1 : 2) : 0;
+  static constexpr int kRawFit = WBITS == 4 ? (int)((kBudget - kSlots * kSlot) / kRawBytes) : 0;
+  static constexpr int kRaw = WBITS == 4 ? std::min(10, kGroups == 2 ? (kRawFit & ~1) : kRawFit) : 0;
+  static constexpr int kAccCols = kATmem ? kATmemCol0 : kTmemCols;
   static constexpr int kRegions = std::min(2 * kMaxAcc, kAccCols / NCOLS);   // accumulators that fit in TMEM
   // two accumulators of a block-128 slot share one hand-over between MMA issuer and drain warps
   static constexpr bool kPair = kRegions >= 4;
   static constexpr int kTokens = NCOLS / 3;
-  static constexpr int kThreads = WBITS == 4 ? 512 : 256;
+  static constexpr int kThreads = 256 + 128 * kGroups;
   static constexpr size_t kSmem = 1024 + (size_t)kRaw * kRawBytes + (size_t)kSlots * kSlot + 1024;
-  static_assert(kSlots >= 2 && (WBITS == 8 || (kRaw >= 2 && kSlots % 2 == 0)), "ring depths");
+  static_assert(kSlots >= 2 && (WBITS == 8 || kRaw >= 2), "ring depths");
+  static_assert(kGroups != 2 || (kSlots % 2 == 0 && kRaw % 2 == 0), "a ring slot always belongs to the same group");
   static_assert(kRegions >= 2, "two accumulators, so that drain and MMA overlap");
-  static_assert(kSmem <= 227 * 1024, "shared memory budget");
+  static_assert(kSmem <= (kOcc == 2 ? 110 * 1024 : 227 * 1024), "shared memory budget");
 };
 
 // The (tile, unit range) fragments of this CTA's share of the stream-K schedule, in order.
@@ -203,14 +216,49 @@ __device__ __forceinline__ void load8<__half>(const __half* p, float* v) {
   }
 }
 
+// 2^(21-e) and 2^(e-21) * pw_mul for a row whose largest |x| has the float bits `mx`; a row with a non-finite entry
+// gets (0, NaN), an all-zero or denormal row any small exponent.
+__device__ __forceinline__ void row_factors(uint32_t mx, float pw_mul, float& mult, float& pw) {
+  int e = (int)(mx >> 23) - 127;
+  const bool finite = e < 128;
+  if (e < -100) e = -100;
+  mult = finite ? __uint_as_float((uint32_t)(21 - e + 127) << 23) : 0.f;
+  pw = finite ? __uint_as_float((uint32_t)(e - 21 + 127) << 23) * pw_mul : __uint_as_float(0x7fc00000u);
+}
+
+// Eight values -> the bytes of their three limbs, packed in k order (two words per limb).
+// X = rint(v * mult) comes out of one FMA against 1.5 * 2^23 (the sum lands where fp32 spacing is 1, so the FMA's
+// round-to-nearest-even IS the rint, and X sits in the low mantissa bits).  Balanced limbs l_i in [-128,127] with
+// X = l0 + 256 l1 + 65536 l2 are the base-256 digits of X + 0x808080, each minus 128: one integer add puts the digits
+// into bytes 0..2, one XOR with 0x808080 turns digit into limb.  Three instructions per value, then byte gathers.
+__device__ __forceinline__ void split8(const float* v, float mult, uint32_t* l0, uint32_t* l1, uint32_t* l2) {
+  uint32_t z[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    z[i] = (__float_as_uint(fmaf(v[i], mult, 12582912.f)) + (0x808080u - 0x4B400000u)) ^ 0x808080u;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t a = z[4 * h], b = z[4 * h + 1], c = z[4 * h + 2], d = z[4 * h + 3];
+    // byte j of a/b in the low half, of c/d in the high half
+    const uint32_t ab0 = __byte_perm(a, b, 0x0040), cd0 = __byte_perm(c, d, 0x0040);
+    const uint32_t ab1 = __byte_perm(a, b, 0x0051), cd1 = __byte_perm(c, d, 0x0051);
+    const uint32_t ab2 = __byte_perm(a, b, 0x0062), cd2 = __byte_perm(c, d, 0x0062);
+    l0[h] = __byte_perm(ab0, cd0, 0x5410);
+    l1[h] = __byte_perm(ab1, cd1, 0x5410);
+    l2[h] = __byte_perm(ab2, cd2, 0x5410);
+  }
+}
+
 // One CTA per token row.  xl: [3*M][K] int8, row 3*m + l = limb l of token m; pw[m] = 2^(e_m - 21) * pw_mul.
 // A row with a non-finite entry gets pw = NaN (its outputs are NaN); an all-zero row gets zeros.
 template <typename XT>
 __global__ void __launch_bounds__(1024) split_rows_kernel(const XT* __restrict__ x, int8_t* __restrict__ xl, float* __restrict__ pw,
                                                           int64_t K, int perm4, float pw_mul) {
   __shared__ uint32_t s_max[32];
+  if (blockIdx.x == 0 && threadIdx.x == 0) { DBG_STAMP(10); }
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");  // x may come from the previous kernel of the stream
+  if (blockIdx.x == 0 && threadIdx.x == 0) { DBG_STAMP(11); }
   const int m = blockIdx.x;
   const XT* xr = x + (int64_t)m * K;
   const int64_t groups = K >> 3;
@@ -233,29 +281,17 @@ __global__ void __launch_bounds__(1024) split_rows_kernel(const XT* __restrict__
   }
   __syncthreads();
   mx = s_max[0];
-  int e = (int)(mx >> 23) - 127;  // exponent of the row maximum
-  const bool finite = e < 128;
-  if (e < -100) e = -100;         // zero / denormal rows: any small exponent represents them exactly enough
-  const float mult = finite ? __uint_as_float((uint32_t)(21 - e + 127) << 23) : 0.f;  // 2^(21-e)
-  if (threadIdx.x == 0) pw[m] = finite ? __uint_as_float((uint32_t)(e - 21 + 127) << 23) * pw_mul : __uint_as_float(0x7fc00000u);
+  float mult, pwv;
+  row_factors(mx, pw_mul, mult, pwv);
+  if (threadIdx.x == 0) pw[m] = pwv;
   int8_t* r0 = xl + (int64_t)(3 * m) * K;
   int8_t* r1 = r0 + K;
   int8_t* r2 = r1 + K;
   for (int64_t gi = threadIdx.x; gi < groups; gi += blockDim.x) {
     float v[8];
     load8<XT>(xr + gi * 8, v);
-    uint32_t l0[2] = {0, 0}, l1[2] = {0, 0}, l2[2] = {0, 0};  // bytes of limb l for k = 8*gi + i, packed in k order
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int X = __float2int_rn(v[i] * mult);
-      const int a0 = (int)(int8_t)(X & 0xff);
-      const int X1 = (X - a0) >> 8;
-      const int a1 = (int)(int8_t)(X1 & 0xff);
-      const int a2 = (X1 - a1) >> 8;
-      l0[i >> 2] |= (uint32_t)(a0 & 0xff) << (8 * (i & 3));
-      l1[i >> 2] |= (uint32_t)(a1 & 0xff) << (8 * (i & 3));
-      l2[i >> 2] |= (uint32_t)(a2 & 0xff) << (8 * (i & 3));
-    }
+    uint32_t l0[2], l1[2], l2[2];  // bytes of limb l for k = 8*gi + i, packed in k order
+    split8(v, mult, l0, l1, l2);
     if (!perm4) {
       const int64_t o = gi * 8;
       *reinterpret_cast<uint2*>(r0 + o) = make_uint2(l0[0], l0[1]);
@@ -274,6 +310,7 @@ __global__ void __launch_bounds__(1024) split_rows_kernel(const XT* __restrict__
       *reinterpret_cast<uint32_t*>(r2 + base + 16) = odds(l2);
     }
   }
+  if (blockIdx.x == 0 && threadIdx.x == 0) { DBG_STAMP(12); }
 }
 
 // ---- the stream-K tensor-core kernel -----------------------------------------------------------------------------
@@ -301,7 +338,7 @@ __device__ __forceinline__ void fold_region(uint32_t taddr, float sc, float (&to
 }
 
 template <int WBITS, int NCOLS>
-__global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, 1)
+__global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, Cfg<WBITS, NCOLS>::kOcc)
     limb_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const Params p) {
   using C = Cfg<WBITS, NCOLS>;
   constexpr int kRaw = C::kRaw, kSlots = C::kSlots;
@@ -327,6 +364,10 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, 1)
   const long long dbg_k0 = clock64();
   const unsigned long long dbg_g0 = ptx::globaltimer_ns();
 #endif
+  if (threadIdx.x == 0) { DBG_STAMP(0); }
+#ifdef QMM_LIMB_DBG
+  if (threadIdx.x == 0 && blockIdx.x < 512) g_limb_cta[4 * blockIdx.x] = (long long)ptx::globaltimer_ns();
+#endif
   // accumulators per hand-over and hand-over buffers in the TMEM ring
   const int gph = (p.mode == kBlock128 && C::kPair) ? 2 : 1;
   const int nacc = min(kMaxAcc, C::kRegions / gph);
@@ -337,7 +378,9 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, 1)
       ptx::mbar_init(&raw_empty[s], 4);
     }
     for (int s = 0; s < kSlots; ++s) {
-      ptx::mbar_init(&full[s], WBITS == 4 ? 5 : 2);
+      // arrivals per slot: the weight side (int8: the TMA producer; int4: the four expanding warps of the slot's group)
+      // and the limb tiles' TMA producer
+      ptx::mbar_init(&full[s], (WBITS == 4 ? 4 : 1) + 1);
       ptx::mbar_init(&empty[s], 1);
     }
     for (int s = 0; s < kMaxAcc; ++s) {
@@ -350,13 +393,14 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, 1)
     ptx::prefetch_tensormap(&map_x);
   }
   if (warp == 1) {
-    ptx::tmem_alloc(tmem_slot, 512);
+    ptx::tmem_alloc(tmem_slot, C::kTmemCols);
     ptx::tmem_relinquish();
   }
   ptx::tcgen05_fence_before();
   __syncthreads();
   ptx::tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) { DBG_STAMP(1); }
   // The next kernel of the stream may start its own set-up now; it touches nothing of ours before its own wait.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
@@ -395,6 +439,7 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, 1)
     // ---------------- limb tile producer ----------------
     if (lane == 0) {
       asm volatile("griddepcontrol.wait;" ::: "memory");  // the limbs are written by the kernel before this one
+      DBG_STAMP(2);
       FragIter it(p);
       DBG_DECL;
       int tile, u0, u1, slot = 0;
@@ -452,10 +497,19 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, 1)
       ptx::mma_commit_pred(&acc_full[buf], leader);
       if (++buf == nacc) { buf = 0; pacc ^= 1; }
     };
+    bool dbg_first = true;
+    (void)dbg_first;
     auto wait_slot = [&]() {
       DBG_BEGIN();
       ptx::mbar_wait(&full[slot], ph, abort_flag, p.err_word, ptx::kErrWaitFull);
       DBG_END(1);
+      if (dbg_first) {
+        DBG_STAMP(3);
+#ifdef QMM_LIMB_DBG
+        if (lane == 0 && blockIdx.x < 512) g_limb_cta[4 * blockIdx.x + 1] = (long long)ptx::globaltimer_ns();
+#endif
+        dbg_first = false;
+      }
       ptx::tcgen05_fence_after();
     };
     auto next_slot = [&]() {
@@ -504,10 +558,15 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, 1)
         }
       }
     }
+    DBG_STAMP(4);
+#ifdef QMM_LIMB_DBG
+    if (lane == 0 && blockIdx.x < 512) g_limb_cta[4 * blockIdx.x + 2] = (long long)ptx::globaltimer_ns();
+#endif
     DBG_FLUSH(16);
   } else if (warp >= kDrainWarp0 && warp < kDrainWarp0 + 4) {
     // ---------------- drain: thread = one weight row n (its TMEM lane) ----------------
     asm volatile("griddepcontrol.wait;" ::: "memory");  // pw, the scratch and `out` belong to earlier kernels until here
+    if (warp == kDrainWarp0) { DBG_STAMP(5); }
     const int quad = warp & 3;
     const int rl = quad * 32 + lane;  // row inside the tile
     const int dt = threadIdx.x - kDrainWarp0 * 32;  // 0..127 among the drain threads
@@ -674,6 +733,7 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, 1)
       }
       DBG_END(2);
     }
+    if (warp == kDrainWarp0) { DBG_STAMP(6); }
     if (warp == kDrainWarp0) { DBG_FLUSH(24); }
   } else if (WBITS == 4 && warp >= kConvWarp0) {
     // ---------------- int4: nibble -> high half of a byte (value * 16 as int8); lane = row ----------------
@@ -691,7 +751,7 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, 1)
     while (it.next(tile, u0, u1)) {
       const int s0 = u0 * p.spu, s1 = min(p.slots, u1 * p.spu);
       for (int s = s0; s < s1; ++s, ++i) {
-        if ((int)(i & 1) != grp) continue;
+        if (C::kGroups == 2 && (int)(i & 1) != grp) continue;
         const uint32_t sr = i % kRaw, pr = (i / kRaw) & 1, sa = i % kSlots, pa = (i / kSlots) & 1;
         DBG_BEGIN();
         ptx::mbar_wait_warp<32>(&raw_full[sr], pr, abort_flag, p.err_word, ptx::kErrWaitRaw);
@@ -744,11 +804,15 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, 1)
   if (blockIdx.x == 0 && threadIdx.x == 0) {
     g_limb_dbg[40] = clock64() - dbg_k0;
     g_limb_dbg[41] = (long long)(ptx::globaltimer_ns() - dbg_g0);
+    DBG_STAMP(7);
+  }
+  if (threadIdx.x == 0 && blockIdx.x < 512) {
+    g_limb_cta[4 * blockIdx.x + 3] = (long long)ptx::globaltimer_ns();
   }
 #endif
   if (warp == 1) {
     ptx::tcgen05_fence_after();
-    ptx::tmem_dealloc(tmem_base, 512);
+    ptx::tmem_dealloc(tmem_base, C::kTmemCols);
   }
 }
 
@@ -912,9 +976,31 @@ int launch_limb_tc(int wbits, const void* x, int x_dt, const void* w, const floa
   p.flags = sc.flags;
   p.err_word = device_error_word();
   p.gate_up = gate_up;
-  // every CTA should stream at least a few slots, or the fixed cost of a CTA (set-up, partial exchange) dominates
+  // Work split.  Stream-K (equal shares of the tile x K-slot units) keeps every SM streaming, but a tile shared by
+  // several CTAs costs a partial-tile exchange through L2 at the end of the kernel, worth a few slots of streaming.
+  // When handing out whole tiles costs fewer slots per CTA than that, each CTA gets whole tiles and nothing is
+  // exchanged.  Every CTA should stream at least two slots, or its fixed cost dominates.
+  const int occ = (wbits == 4 && ncols <= 48) ? 2 : 1;  // Cfg::kOcc
+  const long long ctas_max = std::min<long long>((long long)occ * sm_count(), kLimbMaxCtas);
   const long long min_units = std::max<long long>(1, 2 / p.spu);
-  int grid = (int)std::min<long long>(std::min(sm_count(), kLimbMaxCtas), std::max<long long>(1, p.units / min_units));
+  int grid = (int)std::min<long long>(ctas_max, std::max<long long>(1, p.units / min_units));
+  {
+    const long long sk_slots = ceil_div(p.units, grid) * p.spu;                 // slots per CTA, stream-K
+    const long long per_sm = occ;                                               // CTAs that share an SM's bandwidth
+    const long long dp_rounds = ceil_div(p.tiles, ctas_max);
+    const long long dp_slots = dp_rounds * p.slots;                             // slots per CTA, whole tiles
+    // exchange cost in slots of streaming (measured); a partial tile is 128 x M floats, so it grows with the batch
+    const long long exchange = (wbits == 4 ? 8 : 4) * std::max(1, ncols / 48);
+    // compare per-SM streaming: with whole tiles only ceil(tiles / rounds) CTAs run, spread over the SMs
+    const long long dp_ctas = ceil_div(p.tiles, dp_rounds);
+    const long long dp_per_sm = ceil_div(dp_ctas, sm_count());
+    const bool fills = occ == 1 || dp_ctas * 4 >= ctas_max * 3;  // two CTAs per SM only pay off when both slots are used
+    if (fills && dp_slots * dp_per_sm <= sk_slots * per_sm + exchange && p.tiles <= ctas_max * dp_rounds) {
+      grid = (int)std::min<long long>(p.tiles, ctas_max);
+      // with several rounds the units must still split at tile boundaries: a grid that divides the tile count
+      while (p.tiles % grid != 0) --grid;
+    }
+  }
 
   CUtensorMap map_w, map_x;
   int rc = encode_tmap_2d(&map_w, w, 1, false, (uint64_t)N, (uint64_t)(K * wbits / 8), BMW, 128);
@@ -923,22 +1009,17 @@ int launch_limb_tc(int wbits, const void* x, int x_dt, const void* w, const floa
   if (rc != QMM_OK) return rc;
 
   const float pw_mul = wbits == 4 ? 0.0625f : 1.f;
-  cudaError_t e;
-  static const int skip_split = getenv("QMM_EXP_SKIP_SPLIT") ? atoi(getenv("QMM_EXP_SKIP_SPLIT")) : 0;
-  if (skip_split == 2) {  // split only
-    if (x_dt == QMM_BF16) e = launch_split<__nv_bfloat16>(x, sc.limbs, sc.pw, M, K, wbits == 4, pw_mul, st);
-    return QMM_OK;
-  }
-  if (skip_split == 1) {
-    if (wbits == 4) return launch_ncols<4>(ncols, map_w, map_x, p, grid, st);
-    return launch_ncols<8>(ncols, map_w, map_x, p, grid, st);
-  }
-  if (x_dt == QMM_F32) e = launch_split<float>(x, sc.limbs, sc.pw, M, K, wbits == 4, pw_mul, st);
-  else if (x_dt == QMM_BF16) e = launch_split<__nv_bfloat16>(x, sc.limbs, sc.pw, M, K, wbits == 4, pw_mul, st);
-  else e = launch_split<__half>(x, sc.limbs, sc.pw, M, K, wbits == 4, pw_mul, st);
-  if (e != cudaSuccess) {
-    cudaGetLastError();
-    return fail(QMM_ERR_LAUNCH, "split_rows_kernel launch: %s", cudaGetErrorString(e));
+  {
+    // the limbs are made by a kernel of their own (one CTA per token) and reach the main kernel as TMA tiles; the two
+    // are chained with programmatic dependent launch, so the main kernel's set-up and first weight loads run under it
+    cudaError_t e;
+    if (x_dt == QMM_F32) e = launch_split<float>(x, sc.limbs, sc.pw, M, K, wbits == 4, pw_mul, st);
+    else if (x_dt == QMM_BF16) e = launch_split<__nv_bfloat16>(x, sc.limbs, sc.pw, M, K, wbits == 4, pw_mul, st);
+    else e = launch_split<__half>(x, sc.limbs, sc.pw, M, K, wbits == 4, pw_mul, st);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(QMM_ERR_LAUNCH, "split_rows_kernel launch: %s", cudaGetErrorString(e));
+    }
   }
   int rcl = wbits == 4 ? launch_ncols<4>(ncols, map_w, map_x, p, grid, st) : launch_ncols<8>(ncols, map_w, map_x, p, grid, st);
   return rcl;
@@ -955,6 +1036,24 @@ extern "C" __attribute__((visibility("default"))) void qmm_debug_limb_dump() {
   for (int r = 0; r < 5; ++r)
     fprintf(stderr, "[dbg] %-6s w0=%lld w1=%lld w2=%lld w3=%lld total=%lld\n", names[r], h[8 * r], h[8 * r + 1], h[8 * r + 2],
             h[8 * r + 3], h[8 * r + 4]);
+  fprintf(stderr, "[dbg] timeline (us after entry): setup %.2f | prev-kernel-done(B) %.2f | first slot full %.2f | MMAs issued %.2f | drain start %.2f | drain end %.2f | exit %.2f || split: entry %.2f wait-done %.2f end %.2f\n",
+          (h[43] - h[42]) * 1e-3, (h[44] - h[42]) * 1e-3, (h[45] - h[42]) * 1e-3, (h[46] - h[42]) * 1e-3, (h[47] - h[42]) * 1e-3,
+          (h[48] - h[42]) * 1e-3, (h[49] - h[42]) * 1e-3, (h[52] - h[42]) * 1e-3, (h[53] - h[42]) * 1e-3, (h[54] - h[42]) * 1e-3);
+  {
+    static long long c[4 * 512];
+    cudaMemcpyFromSymbol(c, qmm::g_limb_cta, sizeof(c));
+    long long t0 = 0;
+    int n = 0;
+    for (int i = 0; i < 512; ++i)
+      if (c[4 * i + 3] > 0) { ++n; if (t0 == 0 || c[4 * i] < t0) t0 = c[4 * i]; }
+    fprintf(stderr, "[dbg] per-CTA (us after the first entry): cta entry first-full mma-issued exit\n");
+    for (int i = 0; i < n; i += (n > 40 ? n / 20 : 1))
+      fprintf(stderr, "[dbg]   %3d %7.2f %7.2f %7.2f %7.2f\n", i, (c[4 * i] - t0) * 1e-3, (c[4 * i + 1] - t0) * 1e-3, (c[4 * i + 2] - t0) * 1e-3,
+              (c[4 * i + 3] - t0) * 1e-3);
+    double mx = 0, mxe = 0;
+    for (int i = 0; i < n; ++i) { mx = std::max(mx, (c[4 * i + 3] - t0) * 1e-3); mxe = std::max(mxe, (c[4 * i] - t0) * 1e-3); }
+    fprintf(stderr, "[dbg]   %d CTAs, last entry %.2f, last exit %.2f\n", n, mxe, mx);
+  }
   fprintf(stderr, "[dbg] kernel  cycles=%lld ns=%lld -> %.3f GHz\n", h[40], h[41], h[41] ? (double)h[40] / (double)h[41] : 0.0);
 }
 #endif

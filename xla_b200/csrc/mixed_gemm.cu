@@ -52,15 +52,7 @@ struct Params {
   int tiles_per_cta;    // k tiles each CTA of a cluster takes (== k_tiles without split-K)
   int blockwise;
   uint32_t* err_word;
-  long long* trace;  // optional pipeline timestamps of CTA (0,0,0), see qmm_debug_set_trace
 };
-
-// Per-role event log: role r writes clock64() stamps to trace[r * kTraceStride + i].
-constexpr int kTraceStride = 1024;
-__device__ __forceinline__ void stamp(const Params& p, int role, int& idx) {
-  if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && idx < kTraceStride)
-    p.trace[role * kTraceStride + idx++] = clock64();
-}
 
 // Ring depths per weight width and token-tile width.  Decode-sized tiles are HBM-bound: deep raw-weight
 // and operand rings, activation tiles grouped per barrier.  Prefill-sized tiles are tensor-bound and spend
@@ -272,12 +264,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (warp == 0) {
     // ---------------- raw weight producer ----------------
     if (lane == 0) {
-      int ti = 0;
       const int byte0 = tile0 * (BK * WBITS / 8);
       for (int r = 0; r < n_raw; ++r) {
         const int s = r % kRawStages;
         ptx::mbar_wait<64>(&raw_empty[s], ((r / kRawStages) & 1) ^ 1, abort_flag, p.err_word, ptx::kErrWaitEmpty);
-        stamp(p, 3, ti);
         ptx::mbar_expect_tx(&raw_full[s], kRawBytes);
         ptx::tma_load_2d(raw_base + (size_t)s * kRawBytes, &map_w, &raw_full[s], byte0 + r * 128, (int32_t)n0);
       }
@@ -311,7 +301,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t desc_hi = (uint32_t)(ptx::make_sw128_kmajor_desc(0) >> 32);
       const uint32_t a_lo0 = (uint32_t)ptx::make_sw128_kmajor_desc(ptx::smem_u32(a_base));
       const uint32_t b_lo0 = (uint32_t)ptx::make_sw128_kmajor_desc(ptx::smem_u32(b_base));
-      int blk = 0, in_blk = 0, ti = 0;
+      int blk = 0, in_blk = 0;
       const uint32_t leader = lane == 0 ? 1u : 0u;
       // ring positions advance with adds and compares only: this warp's instruction count per tile is what
       // bounds the kernel at small token tiles, and a division by a ring depth costs as much as an MMA issue
@@ -325,9 +315,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           ptx::tcgen05_fence_after();  // the drain warps' tcgen05.ld of this buffer precede the overwrite
         }
         if (jb == 0) ptx::mbar_wait(&b_full[sb], b_par, abort_flag, p.err_word, ptx::kErrWaitFull);
-        if (p.trace && lane == 0) stamp(p, 1, ti);
         ptx::mbar_wait(&a_full[sa], a_par, abort_flag, p.err_word, ptx::kErrWaitConv);
-        if (p.trace && lane == 0) stamp(p, 1, ti);
         const bool last_in_block = (in_blk + 1 == p.tiles_per_block) || (t == my_tiles - 1);
         const uint32_t d_tmem = tmem_base + buf * MP;
 #pragma unroll
@@ -340,7 +328,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         const bool group_done = (jb == kBGroup - 1) || (t == my_tiles - 1);
         if (group_done) ptx::mma_commit_pred(&b_empty[sb], leader);
         if (last_in_block) ptx::mma_commit_pred(&acc_full[buf], leader);
-        if (p.trace && lane == 0) stamp(p, 1, ti);
         ++in_blk;
         if (last_in_block) {
           in_blk = 0;
@@ -373,15 +360,11 @@ __global__ void __launch_bounds__(kThreads, 1)
     constexpr int kActive = kDequantWarps;
     constexpr int kChunks = (WBITS == 4) ? 2 : 4;  // 16-byte raw chunks per row per operand tile
     const int dw = (warp - 4) - ((warp - 4) + 3) / 4;  // warps 4,6,7,8,10,11 -> 0..5
-    int ti = 0;
-    const bool tracer = (warp == 4 && lane == 0);
     for (int t = dw; t < my_tiles; t += kActive) {
       const int rs = t / TPR, a = t % TPR;
       const int s = rs % kRawStages, sa = t % kAStages;
-      if (tracer) stamp(p, 0, ti);
       ptx::mbar_wait_warp<64>(&a_empty[sa], ((t / kAStages) & 1) ^ 1, abort_flag, p.err_word, ptx::kErrWaitEmpty);
       ptx::mbar_wait_warp<64>(&raw_full[s], (rs / kRawStages) & 1, abort_flag, p.err_word, ptx::kErrWaitRaw);
-      if (tracer) stamp(p, 0, ti);
       const uint8_t* raw_tile = raw_base + (size_t)s * kRawBytes;
       uint8_t* a_tile = a_base + (size_t)sa * kABytes;
       // all loads of the tile first (plain loads: the compiler may keep them in flight together), then
@@ -432,7 +415,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         ptx::mbar_arrive(&a_full[sa]);
         ptx::mbar_arrive(&raw_empty[s]);
       }
-      if (tracer) stamp(p, 0, ti);
     }
   } else if (warp >= 12) {
     // ---------------- drain / epilogue: thread owns output column n = n0 + its TMEM lane ----------------
@@ -447,15 +429,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       float acc[MP];
 #pragma unroll
       for (int j = 0; j < MP; ++j) acc[j] = 0.f;
-      int ti = 0;
-      const bool tracer = (warp == 12 && lane == 0);
       for (int b = 0; b < n_blocks; ++b) {
         const int buf = b & 1;
         const float s = n_ok ? (p.blockwise ? __ldg(p.scale + (int64_t)(block0 + b) * p.N + n) : 1.f) : 0.f;
-        if (tracer) stamp(p, 2, ti);
         ptx::mbar_wait_warp<32>(&acc_full[buf], (b >> 1) & 1, abort_flag, p.err_word, ptx::kErrWaitTmemFull);
         ptx::tcgen05_fence_after();
-        if (tracer) stamp(p, 2, ti);
 #pragma unroll
         for (int c = 0; c < MP / 16; ++c) {
           uint32_t rr[16];
@@ -467,7 +445,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         ptx::tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&acc_empty[buf]);
-        if (tracer) stamp(p, 2, ti);
       }
       if constexpr (KSPLIT) {
         // (1) every CTA of the cluster is past its main loop: the leader's rings may be overwritten
@@ -639,7 +616,6 @@ int launch_mixed_tc(int wbits, const void* x, int x_dt, const void* w, const flo
   p.tiles_per_block = blockwise ? (int)(block_size / BK) : p.k_tiles;
   p.blockwise = blockwise ? 1 : 0;
   p.err_word = device_error_word();
-  p.trace = debug_trace_buffer();
   const int64_t n_tiles = ceil_div(N, BMW), m_tiles = ceil_div(M, mp);
   if (m_tiles > 65535) return fail(QMM_ERR_UNSUPPORTED, "weight-only tcgen05 kernel: M too large");
   // split K over a cluster when the (n, m) tiles alone leave most SMs idle; the leader needs room for
