@@ -329,15 +329,8 @@ def _rand_i8(gen, dev, n, k):
 def _variant_name(wbits, M, N, K, bs):
   from xla_b200 import _capi
   L = _capi.lib()
-  names = {3: "tcgen05", 4: "mma", 6: "i8tc"}
-  t = L.qmm_tuned_variant(wbits, M, N, K, bs)
-  if t in names:
-    return names[t] + " (tuned table)"
-  op = _capi.OP_W8A16_PERCHANNEL if wbits == 8 else _capi.OP_W4A16_BLOCKWISE_PACKED
-  name = L.qmm_variant_for(op, M, N, K, bs, 0).decode()
-  if M <= 64 and N * K >= (1 << 20):
-    name = "i8tc"
-  return name + " (shape rule)"
+  name = L.qmm_weight_only_variant_for(wbits, M, N, K, bs, 0).decode()
+  return name + (" (tuned table)" if L.qmm_tuned_variant(wbits, M, N, K, bs) else " (shape rule)")
 
 
 def other_configs(dev, stream, peaks, seed):

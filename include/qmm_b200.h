@@ -160,6 +160,8 @@ QMM_API size_t qmm_weight_only_workspace_size(int64_t max_M, int64_t K);
  * Replaces: get_tuned_block_sizes (torch_xla/experimental/pallas_kernels/quantized_matmul_kernel.py:537-555).
  */
 QMM_API int qmm_tuned_variant(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size);
+/* Name of the kernel family qmm_weight_only's AUTO picks for a shape, given a sufficient workspace (static string). */
+QMM_API const char* qmm_weight_only_variant_for(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size, int has_zp);
 QMM_API int qmm_weight_only(int wbits, const void* x, int x_dtype, const void* w, const float* scale, const float* zp,
                     void* out, int out_dtype, int64_t M, int64_t N, int64_t K, int64_t block_size, int variant,
                     void* workspace, size_t workspace_bytes, void* stream);

@@ -72,6 +72,24 @@ def test_ragged_shapes(N, K, wbits, bs, M):
   assert qo.max_abs_rel(out, _exact(x, w, s, bs)) < TOL_F32
 
 
+# larger batches run as (weight tile, token tile) items with 42 tokens per tile; 1008 tokens per launch
+@pytest.mark.parametrize("M", [65, 84, 85, 126, 127, 300, 512, 1008, 1009, 1100])
+@pytest.mark.parametrize("wbits,bs", [(8, 0), (4, 128), (8, 128), (4, 0), (8, 512)])
+def test_large_batches(M, wbits, bs):
+  g = qc.gen(300 + M)
+  N, K = 900, 1536
+  x = qc.activations(g, M, K, outliers=True)
+  w = qc.int4_weight(g, N, K) if wbits == 4 else qc.int8_weight(g, N, K)
+  s = qc.blockwise_scale(g, K // bs, N) if bs > 0 else qc.per_channel_scale(g, N)
+  exact = _exact(x, w, s, bs)
+  out = _run(x, w, s, bs, wbits, torch.float32)
+  assert tuple(out.shape) == (M, N)
+  assert qo.max_abs_rel(out, exact) < TOL_F32
+  if M in (127, 512):
+    out16 = _run(x, w, s, bs, wbits, torch.bfloat16)
+    assert qo.max_abs_rel(out16, exact) < TOL_BF16
+
+
 @pytest.mark.parametrize("xdt", [torch.float32, torch.float16, torch.bfloat16])
 def test_activation_dtypes_and_ranges(xdt):
   g = qc.gen(7)

@@ -31,6 +31,7 @@ SIGNATURES = {
     "qmm_w8a16_blockwise": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _p]),
     "qmm_weight_only_workspace_size": (_sz, [_i64, _i64]),
     "qmm_tuned_variant": (_i, [_i, _i64, _i64, _i64, _i64]),
+    "qmm_weight_only_variant_for": (ctypes.c_char_p, [_i, _i64, _i64, _i64, _i64, _i]),
     "qmm_weight_only": (_i, [_i, _p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _p, _sz, _p]),
     "qmm_host_pipeline_create": (_i, [_sz, _sz, _i, ctypes.POINTER(ctypes.c_void_p)]),
     "qmm_host_weight_only": (_i, [_p, _i, _p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i]),
@@ -129,7 +130,7 @@ def workspace(device, max_M, K):
   """Scratch for ``qmm_weight_only`` on torch's current stream of `device`: (pointer, bytes), or (None, 0) when no
   variant needs one.  One buffer per (device, stream), zero-filled when created (the kernels keep its flag words
   zero) and grown on demand; a stream capture in progress never allocates - it gets the existing buffer or none."""
-  need = lib().qmm_weight_only_workspace_size(min(max_M, 64), K)
+  need = lib().qmm_weight_only_workspace_size(max_M, K)
   if need == 0:
     return None, 0
   idx = device.index if device.index is not None else torch.cuda.current_device()

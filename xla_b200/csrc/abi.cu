@@ -325,8 +325,22 @@ int qmm_tuned_variant(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_
   return tuned_variant(wbits, block_size < 0 ? 0 : block_size, M, N, K);
 }
 
+const char* qmm_weight_only_variant_for(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size, int has_zp) {
+  // Shape-only view of qmm_weight_only's AUTO choice, for a caller that passes a sufficient workspace and aligned pointers.
+  if (block_size < 0) block_size = 0;
+  const void* ok = reinterpret_cast<const void*>(uintptr_t(256));
+  const bool can = limb_tc_shape_ok(wbits, M, N, K, block_size, QMM_BF16, has_zp != 0);
+  const int tuned = tuned_variant(wbits, block_size, M, N, K);
+  if (can && (tuned ? tuned == QMM_VARIANT_I8TC : limb_tc_preferred(wbits, M, N, K, block_size))) return "i8tc";
+  if (!has_zp && tuned == QMM_VARIANT_MMA && decode_mma_supported(wbits, M, N, K, block_size, ok, QMM_BF16, ok, false)) return "mma";
+  if (!has_zp && tuned == QMM_VARIANT_TCGEN05 && mixed_tc_shape_ok(wbits, M, N, K, block_size, QMM_BF16, false)) return "tcgen05";
+  if (decode_mma_supported(wbits, M, N, K, block_size, ok, QMM_BF16, ok, has_zp != 0)) return "mma";
+  if (mixed_tc_shape_ok(wbits, M, N, K, block_size, QMM_BF16, has_zp != 0)) return "tcgen05";
+  if (gemv_nk_supported(wbits, M, N, K, block_size, ok, QMM_BF16, ok)) return "gemv";
+  return "generic";
+}
+
 size_t qmm_weight_only_workspace_size(int64_t max_M, int64_t K) {
-  if (max_M > 64) max_M = 64;  // larger batches never use the scratch
   return limb_tc_workspace_bytes(max_M, K);
 }
 

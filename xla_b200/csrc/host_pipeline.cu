@@ -159,7 +159,7 @@ extern "C" int qmm_host_weight_only(void* pipeline, int layout, const void* x_ho
     default: return qmm::fail(QMM_ERR_UNSUPPORTED, "host_weight_only: unknown weight layout %d", layout);
   }
   if (blockwise && block_size <= 0) return qmm::fail(QMM_ERR_BAD_SHAPE, "host_weight_only: blockwise layout needs block_size > 0");
-  const size_t ws_need = M <= 64 ? qmm_weight_only_workspace_size(M, K) : 0;
+  const size_t ws_need = qmm_weight_only_workspace_size(M, K);
   const bool ws_ok = ws_need > 0 && ws_need <= p->ws_bytes;
   const int rc = qmm_weight_only(wbits, p->xd[slot], x_dtype, w, scale, zp, p->yd[slot], out_dtype, M, N, K, blockwise ? block_size : 0,
                                  variant, ws_ok ? p->ws : nullptr, ws_ok ? p->ws_bytes : 0, p->s_k);

@@ -106,6 +106,8 @@ struct Params {
   uint32_t* flags;  // [grid], zero between launches
   uint32_t* err_word;
   int gate_up;
+  int ytiles;  // > 0: work items are (weight tile, token tile) pairs with the whole K range each; 0: stream-K
+  int m0;      // first token of this launch inside the caller's batch (row offset of `out`)
 };
 
 template <int WBITS, int NCOLS>
@@ -119,12 +121,16 @@ struct Cfg {
   static constexpr int kTmemCols = 512 / kOcc;
   static constexpr uint32_t kBudget = kOcc == 2 ? 110 * 1024 - 2048 : kSmemBudget;
   // int4 with up to 96 limb columns: the expanded weight operand lives in tensor memory (64 columns per slot, in the
-  // upper half of the CTA's columns) and never touches shared memory; the ring slots then hold limb tiles only
+  // upper half of the CTA's columns) and never touches shared memory; the ring slots then hold limb tiles only.
+  // (Wider tiles need the columns for accumulators: with two operand slots and three accumulators the large-batch
+  // tiles measured 20 % slower than with the operand in shared memory.)
   static constexpr bool kATmem = WBITS == 4 && NCOLS <= 96;
-  static constexpr int kATmemCol0 = kTmemCols / 2, kATmemSlotCols = 64;
+  static constexpr int kATmemSlotCols = 64;
+  static constexpr int kATmemSlots = kTmemCols / 2 / kATmemSlotCols;
+  static constexpr int kATmemCol0 = kTmemCols - kATmemSlots * kATmemSlotCols;
   static constexpr uint32_t kAInSlot = kATmem ? 0 : kASlot;
   static constexpr uint32_t kSlot = kAInSlot + 2 * kBTile;   // [A tile 0 | A tile 1 |] B tile 0 | B tile 1
-  static constexpr int kSlots = kATmem ? kATmemCol0 / kATmemSlotCols : (WBITS == 4 ? 2 : std::min<int>(6, kBudget / kSlot));
+  static constexpr int kSlots = kATmem ? kATmemSlots : (WBITS == 4 ? 2 : std::min<int>(6, kBudget / kSlot));
   // expanding warps: two groups of four that take alternate slots, or one group where two CTAs share the SM
   static constexpr int kGroups = WBITS == 4 ? (kOcc == 2 ? 1 : 2) : 0;
   static constexpr int kRawFit = WBITS == 4 ? (int)((kBudget - kSlots * kSlot) / kRawBytes) : 0;
@@ -134,7 +140,11 @@ struct Cfg {
   // two accumulators of a block-128 slot share one hand-over between MMA issuer and drain warps
   static constexpr bool kPair = kRegions >= 4;
   static constexpr int kTokens = NCOLS / 3;
-  static constexpr int kThreads = 256 + 128 * kGroups;
+  // drain warps: four (one per TMEM lane quadrant), or eight for the large-batch tiles, where the two warps of a
+  // quadrant take half of the tile's tokens each (the per-block rescaling is what bounds that mode)
+  static constexpr int kHalves = NCOLS == 128 ? 2 : 1;
+  static constexpr int kXDrainWarp0 = 8 + 4 * kGroups;
+  static constexpr int kThreads = 256 + 128 * kGroups + 128 * (kHalves - 1);
   static constexpr size_t kSmem = 1024 + (size_t)kRaw * kRawBytes + (size_t)kSlots * kSlot + 1024;
   static_assert(kSlots >= 2 && (WBITS == 8 || kRaw >= 2), "ring depths");
   static_assert(kGroups != 2 || (kSlots % 2 == 0 && kRaw % 2 == 0), "a ring slot always belongs to the same group");
@@ -146,12 +156,27 @@ struct Cfg {
 struct FragIter {
   long long u, hi;
   int ut;
-  __device__ FragIter(const Params& p) : ut(p.ut) {
+  int ytiles, y;          // item mode: number of token tiles, token tile of the current item
+  long long item, items;
+  __device__ FragIter(const Params& p) : ut(p.ut), ytiles(p.ytiles), y(0) {
     const long long G = gridDim.x;
     u = (long long)blockIdx.x * p.units / G;
     hi = (long long)(blockIdx.x + 1) * p.units / G;
+    item = blockIdx.x;
+    items = (long long)p.tiles * p.ytiles;
   }
   __device__ bool next(int& tile, int& u0, int& u1) {
+    if (ytiles) {
+      // Large batches: item i = (weight tile i / ytiles, token tile i % ytiles), CTA c takes items c, c + G, ...;
+      // the token tiles of one weight tile run on neighbouring CTAs at the same time and share its bytes in L2.
+      if (item >= items) return false;
+      tile = (int)(item / ytiles);
+      y = (int)(item - (long long)tile * ytiles);
+      u0 = 0;
+      u1 = ut;
+      item += gridDim.x;
+      return true;
+    }
     if (u >= hi) return false;
     tile = (int)(u / ut);
     u0 = (int)(u - (long long)tile * ut);
@@ -315,7 +340,9 @@ __global__ void __launch_bounds__(1024) split_rows_kernel(const XT* __restrict__
 
 // ---- the stream-K tensor-core kernel -----------------------------------------------------------------------------
 // One accumulator (NCOLS int32 columns of this thread's TMEM lane) -> limbs recombined in fp32, times sc, into total.
-template <int NCOLS, int MT, typename Release>
+// SMALL: every int32 sum is below 2^22 in magnitude (scale blocks of at most 256 values), so 256 * A1 + A0 still fits
+// an int32 and one conversion serves both low limbs.
+template <int NCOLS, int MT, bool SMALL, typename Release>
 __device__ __forceinline__ void fold_region(uint32_t taddr, float sc, float (&total)[MT], bool release_after, Release release) {
   constexpr int kChunks = (NCOLS + 47) / 48;
 #pragma unroll
@@ -329,9 +356,13 @@ __device__ __forceinline__ void fold_region(uint32_t taddr, float sc, float (&to
 #pragma unroll
     for (int t = 0; t < 16; ++t) {
       if (c * 16 + t < MT) {
-        const float f0 = __int2float_rn((int)r[3 * t]), f1 = __int2float_rn((int)r[3 * t + 1]),
-                    f2 = __int2float_rn((int)r[3 * t + 2]);
-        total[c * 16 + t] = fmaf(sc, fmaf(f2, 65536.f, fmaf(f1, 256.f, f0)), total[c * 16 + t]);
+        float lowf;
+        if (SMALL) {
+          lowf = __int2float_rn((int)r[3 * t + 1] * 256 + (int)r[3 * t]);
+        } else {
+          lowf = fmaf(__int2float_rn((int)r[3 * t + 1]), 256.f, __int2float_rn((int)r[3 * t]));
+        }
+        total[c * 16 + t] = fmaf(sc, fmaf(__int2float_rn((int)r[3 * t + 2]), 65536.f, lowf), total[c * 16 + t]);
       }
     }
   }
@@ -385,7 +416,7 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, Cfg<WBITS, NCOLS>
     }
     for (int s = 0; s < kMaxAcc; ++s) {
       ptx::mbar_init(&acc_full[s], 1);
-      ptx::mbar_init(&acc_empty[s], 4);
+      ptx::mbar_init(&acc_empty[s], 4 * C::kHalves);
     }
     *abort_flag = 0;
     ptx::fence_mbar_init();
@@ -452,8 +483,8 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, Cfg<WBITS, NCOLS>
           DBG_END(0);
           uint8_t* dst = slot_base + (size_t)slot * kSlot + C::kAInSlot;
           ptx::mbar_expect_tx(&full[slot], 2 * kBTile);
-          ptx::tma_load_2d(dst, &map_x, &full[slot], s * kSlotK, 0);
-          ptx::tma_load_2d(dst + kBTile, &map_x, &full[slot], s * kSlotK + kTileK, 0);
+          ptx::tma_load_2d(dst, &map_x, &full[slot], s * kSlotK, it.y * (3 * MT));
+          ptx::tma_load_2d(dst + kBTile, &map_x, &full[slot], s * kSlotK + kTileK, it.y * (3 * MT));
           if (++slot == kSlots) { slot = 0; ph ^= 1; }
         }
       }
@@ -563,8 +594,13 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, Cfg<WBITS, NCOLS>
     if (lane == 0 && blockIdx.x < 512) g_limb_cta[4 * blockIdx.x + 2] = (long long)ptx::globaltimer_ns();
 #endif
     DBG_FLUSH(16);
-  } else if (warp >= kDrainWarp0 && warp < kDrainWarp0 + 4) {
-    // ---------------- drain: thread = one weight row n (its TMEM lane) ----------------
+  } else if ((warp >= kDrainWarp0 && warp < kDrainWarp0 + 4) || (C::kHalves == 2 && warp >= C::kXDrainWarp0)) {
+    // ---------------- drain: thread = one weight row n (its TMEM lane), all or half of the tile's tokens ----------------
+    constexpr int MTD = MT / C::kHalves;                      // tokens per drain thread
+    constexpr int DC = C::kHalves == 2 ? 64 : NCOLS;          // accumulator columns a thread loads per block
+    const int half = (C::kHalves == 2 && warp >= C::kXDrainWarp0) ? 1 : 0;
+    const uint32_t col0 = (uint32_t)(half * 3 * MTD);
+    const bool small = p.mode == kBlock128 || (p.mode == kBlockSlots && p.spu == 1);
     asm volatile("griddepcontrol.wait;" ::: "memory");  // pw, the scratch and `out` belong to earlier kernels until here
     if (warp == kDrainWarp0) { DBG_STAMP(5); }
     const int quad = warp & 3;
@@ -596,9 +632,11 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, Cfg<WBITS, NCOLS>
       const int64_t n = (int64_t)tile * BMW + rl;
       const bool n_ok = n < p.N;
       const bool first = u0 == 0, last = u1 == p.ut;
-      float total[MT];
+      const int mt0 = it.y * MT + half * MTD;  // first token this thread owns (0 outside item mode)
+      const int mcount = p.M - mt0;          // tokens from there to the end of the batch
+      float total[MTD];
 #pragma unroll
-      for (int t = 0; t < MT; ++t) total[t] = 0.f;
+      for (int t = 0; t < MTD; ++t) total[t] = 0.f;
       // A tile this CTA starts and others continue: their partial sums are usually there already (every CTA works on
       // its share of a started tile first), so they are fetched now, under the K loop, when all of them have landed;
       // otherwise after it.  The order of the additions is the same either way.
@@ -608,8 +646,8 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, Cfg<WBITS, NCOLS>
         for (int j = 0; j < np; ++j) {
           const float* src = p.partial + ((size_t)(blockIdx.x + 1 + j) * MT) * BMW + rl;
 #pragma unroll
-          for (int t = 0; t < MT; ++t)
-            if (t < p.M) total[t] += __ldcg(src + t * BMW);
+          for (int t = 0; t < MTD; ++t)
+            if (t < mcount) total[t] += __ldcg(src + t * BMW);
         }
         drain_bar();
         for (int j = dt; j < np; j += 128) p.flags[blockIdx.x + 1 + j] = 0u;  // clean for the next launch
@@ -656,9 +694,9 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, Cfg<WBITS, NCOLS>
           if (C::kPair) {
             wait_acc();
             DBG_BEGIN();
-            const uint32_t a = lane_addr + buf * (2 * NCOLS);
-            fold_region<NCOLS, MT>(a, pop_scale(), total, false, release);
-            fold_region<NCOLS, MT>(a + NCOLS, pop_scale(), total, true, release);
+            const uint32_t a = lane_addr + buf * (2 * NCOLS) + col0;
+            fold_region<DC, MTD, true>(a, pop_scale(), total, false, release);
+            fold_region<DC, MTD, true>(a + NCOLS, pop_scale(), total, true, release);
             DBG_END(1);
             next_acc();
           } else {
@@ -666,7 +704,7 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, Cfg<WBITS, NCOLS>
             for (int h = 0; h < 2; ++h) {
               wait_acc();
               DBG_BEGIN();
-              fold_region<NCOLS, MT>(lane_addr + buf * NCOLS, pop_scale(), total, true, release);
+              fold_region<DC, MTD, true>(lane_addr + buf * NCOLS + col0, pop_scale(), total, true, release);
               DBG_END(1);
               next_acc();
             }
@@ -679,7 +717,8 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, Cfg<WBITS, NCOLS>
           const float sc = p.mode == kPerChannel ? 1.f : pop_scale();
           wait_acc();
           DBG_BEGIN();
-          fold_region<NCOLS, MT>(lane_addr + buf * NCOLS, sc, total, true, release);
+          if (small) fold_region<DC, MTD, true>(lane_addr + buf * NCOLS + col0, sc, total, true, release);
+          else fold_region<DC, MTD, false>(lane_addr + buf * NCOLS + col0, sc, total, true, release);
           DBG_END(1);
           next_acc();
           s = g_end;
@@ -691,8 +730,8 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, Cfg<WBITS, NCOLS>
         // a later K range of a tile that another CTA started: leave the partial sums for that CTA
         float* dst = p.partial + ((size_t)blockIdx.x * MT) * BMW + rl;
 #pragma unroll
-        for (int t = 0; t < MT; ++t)
-          if (t < p.M) __stcg(dst + t * BMW, total[t]);
+        for (int t = 0; t < MTD; ++t)
+          if (t < mcount) __stcg(dst + t * BMW, total[t]);
         __threadfence();
         drain_bar();
         if (dt == 0) st_release_gpu(p.flags + blockIdx.x, 1u);
@@ -719,23 +758,24 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, Cfg<WBITS, NCOLS>
       const float ps = (p.mode != kPerChannel || !n_ok) ? 1.f : __ldg(p.scale + n);
       if (!p.gate_up) {
 #pragma unroll
-        for (int t = 0; t < MT; ++t)
-          if (t < p.M && n_ok) store_from_f32(p.out, (int64_t)t * p.N + n, p.out_dt, total[t] * ps * __ldg(p.pw + t));
+        for (int t = 0; t < MTD; ++t)
+          if (t < mcount && n_ok)
+            store_from_f32(p.out, (int64_t)(p.m0 + mt0 + t) * p.N + n, p.out_dt, total[t] * ps * __ldg(p.pw + mt0 + t));
       } else {
         // rows come in groups of 16: eight gate rows, then the eight up rows of the same outputs
 #pragma unroll
-        for (int t = 0; t < MT; ++t) {
-          const float v = t < p.M ? total[t] * ps * __ldg(p.pw + t) : 0.f;
+        for (int t = 0; t < MTD; ++t) {
+          const float v = t < mcount ? total[t] * ps * __ldg(p.pw + mt0 + t) : 0.f;
           const float u = __shfl_down_sync(0xffffffffu, v, 8);
-          if (t < p.M && n_ok && (rl & 8) == 0)
-            store_from_f32(p.out, (int64_t)t * (p.N >> 1) + gate_up_column(n), p.out_dt, silu_mul(v, u));
+          if (t < mcount && n_ok && (rl & 8) == 0)
+            store_from_f32(p.out, (int64_t)(p.m0 + mt0 + t) * (p.N >> 1) + gate_up_column(n), p.out_dt, silu_mul(v, u));
         }
       }
       DBG_END(2);
     }
     if (warp == kDrainWarp0) { DBG_STAMP(6); }
     if (warp == kDrainWarp0) { DBG_FLUSH(24); }
-  } else if (WBITS == 4 && warp >= kConvWarp0) {
+  } else if (WBITS == 4 && warp >= kConvWarp0 && warp < kConvWarp0 + 4 * C::kGroups) {
     // ---------------- int4: nibble -> high half of a byte (value * 16 as int8); lane = row ----------------
     // Two groups of four warps; group g expands the slots g, g+2, ... of the CTA's sequence (ring depths are even,
     // so a ring slot always belongs to the same group).
@@ -832,8 +872,11 @@ int ncols_for(int64_t M) {
   if (M <= 16) return 48;
   if (M <= 32) return 96;
   if (M <= 64) return 192;
-  return 0;
+  return 128;  // larger batches: token tiles of 42 (126 limb columns), see launch_limb_tc
 }
+
+constexpr int kItemTokens = 42;                    // Cfg<*, 128>::kTokens
+constexpr int64_t kLimbMaxRows = 24 * kItemTokens;  // tokens per launch in item mode (1008); longer batches are chunked
 
 // Layout of the caller's scratch: [flags: 1 KB][pw][limbs][partial tiles]; the flag words come first so that a
 // caller who clears only the head of the buffer clears them.
@@ -848,7 +891,7 @@ Scratch carve(void* base, int64_t M, int64_t K, int max_ctas) {
   s.limbs = reinterpret_cast<int8_t*>(b + off);
   off += align_up((size_t)3 * M * K, 256);
   s.partial = reinterpret_cast<float*>(b + off);
-  off += (size_t)max_ctas * (ncols_for(M) / 3) * BMW * 4;
+  if (M <= 64) off += (size_t)max_ctas * (ncols_for(M) / 3) * BMW * 4;  // item mode exchanges nothing
   s.bytes = off;
   return s;
 }
@@ -890,6 +933,7 @@ int launch_ncols(int ncols, const CUtensorMap& map_w, const CUtensorMap& map_x, 
     case 32: return launch_cfg<WBITS, 32>(map_w, map_x, p, grid, st);
     case 48: return launch_cfg<WBITS, 48>(map_w, map_x, p, grid, st);
     case 96: return launch_cfg<WBITS, 96>(map_w, map_x, p, grid, st);
+    case 128: return launch_cfg<WBITS, 128>(map_w, map_x, p, grid, st);
     default: return launch_cfg<WBITS, 192>(map_w, map_x, p, grid, st);
   }
 }
@@ -912,14 +956,14 @@ cudaError_t launch_split(const void* x, int8_t* xl, float* pw, int64_t M, int64_
 }  // namespace
 
 size_t limb_tc_workspace_bytes(int64_t M, int64_t K) {
-  if (M < 1 || ncols_for(M) == 0 || K < 1) return 0;
-  return carve(nullptr, M, K, kLimbMaxCtas).bytes;
+  if (M < 1 || K < 1) return 0;
+  return carve(nullptr, std::min(M, kLimbMaxRows), K, kLimbMaxCtas).bytes;
 }
 
 bool limb_tc_shape_ok(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size, int x_dt, bool has_zp) {
   if (has_zp) return false;
   if (x_dt != QMM_BF16 && x_dt != QMM_F16 && x_dt != QMM_F32) return false;
-  if (M < 1 || ncols_for(M) == 0 || N < 1 || K < 128) return false;
+  if (M < 1 || N < 1 || K < 128) return false;
   if (wbits == 8 ? (K % 16 != 0) : (K % 32 != 0)) return false;  // TMA row pitches of the weights and the limbs
   // scale blocks of 128 (two per slot) or of whole 256-value slots
   if (block_size > 0 && ((block_size != kTileK && block_size % kSlotK != 0) || K % block_size != 0)) return false;
@@ -937,8 +981,16 @@ bool limb_tc_supported(int wbits, int64_t M, int64_t N, int64_t K, int64_t block
 }
 
 bool limb_tc_preferred(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size) {
-  (void)wbits; (void)M; (void)block_size;
-  return N * K >= (1 << 20);  // below ~1 M weights the launch is latency-bound and the register-dequant kernel wins
+  // Where the measured table has no entry: this kernel's fixed cost (two launches, the stream-K exchange) is paid
+  // back by its streaming rate once the weight is large enough, sooner the larger the batch (thresholds read off
+  // the tuner's measurements over the reference's shape families); above 64 tokens it beats the conversion-based
+  // tensor-core kernel on every shape measured.
+  (void)block_size;
+  const int64_t mib = N * K * wbits / 8 >> 20;
+  if (M > 64) return N * K >= (1 << 20);
+  if (M > 32) return mib >= 24;
+  if (M > 8) return mib >= 32;
+  return mib >= 48;
 }
 
 int launch_limb_tc(int wbits, const void* x, int x_dt, const void* w, const float* scale, void* out, int out_dt, int64_t M,
@@ -946,7 +998,7 @@ int launch_limb_tc(int wbits, const void* x, int x_dt, const void* w, const floa
                    cudaStream_t st) {
   if (!limb_tc_supported(wbits, M, N, K, block_size, x, x_dt, w, false))
     return fail(QMM_ERR_UNSUPPORTED,
-                "split-activation tensor-core kernel: needs an sm_100 device, 1 <= M <= 64, K >= 128 and a multiple of %d, "
+                "split-activation tensor-core kernel: needs an sm_100 device, K >= 128 and a multiple of %d, "
                 "block_size 128 or a multiple of 256, 16-byte aligned x/w, no zero point (M=%lld N=%lld K=%lld bs=%lld)",
                 wbits == 8 ? 16 : 32, (long long)M, (long long)N, (long long)K, (long long)block_size);
   if (gate_up && N % 16 != 0)
@@ -955,8 +1007,22 @@ int launch_limb_tc(int wbits, const void* x, int x_dt, const void* w, const floa
   if (!workspace || workspace_bytes < need)
     return fail(QMM_ERR_WORKSPACE, "split-activation tensor-core kernel needs %zu bytes of workspace, got %zu", need, workspace_bytes);
   if (!aligned(workspace, 256)) return fail(QMM_ERR_MISALIGNED, "workspace must be 256-byte aligned");
+  if (M > kLimbMaxRows) {
+    // long batches run in chunks of whole token tiles that share the scratch (same stream: ordered)
+    if (gate_up) return fail(QMM_ERR_UNSUPPORTED, "fused gate/up epilogue: at most %lld tokens per call", (long long)kLimbMaxRows);
+    const size_t xb = dtype_size(x_dt), ob = dtype_size(out_dt);
+    for (int64_t m0 = 0; m0 < M; m0 += kLimbMaxRows) {
+      const int64_t mc = std::min(kLimbMaxRows, M - m0);
+      const int rc = launch_limb_tc(wbits, reinterpret_cast<const uint8_t*>(x) + (size_t)m0 * K * xb, x_dt, w, scale,
+                                    reinterpret_cast<uint8_t*>(out) + (size_t)m0 * N * ob, out_dt, mc, N, K, block_size, 0, workspace,
+                                    workspace_bytes, st);
+      if (rc != QMM_OK) return rc;
+    }
+    return QMM_OK;
+  }
   const Scratch sc = carve(workspace, M, K, kLimbMaxCtas);
   const int ncols = ncols_for(M);
+  const bool items = M > 64;
 
   Params p;
   p.scale = scale;
@@ -976,15 +1042,21 @@ int launch_limb_tc(int wbits, const void* x, int x_dt, const void* w, const floa
   p.flags = sc.flags;
   p.err_word = device_error_word();
   p.gate_up = gate_up;
-  // Work split.  Stream-K (equal shares of the tile x K-slot units) keeps every SM streaming, but a tile shared by
-  // several CTAs costs a partial-tile exchange through L2 at the end of the kernel, worth a few slots of streaming.
-  // When handing out whole tiles costs fewer slots per CTA than that, each CTA gets whole tiles and nothing is
-  // exchanged.  Every CTA should stream at least two slots, or its fixed cost dominates.
-  const int occ = (wbits == 4 && ncols <= 48) ? 2 : 1;  // Cfg::kOcc
-  const long long ctas_max = std::min<long long>((long long)occ * sm_count(), kLimbMaxCtas);
-  const long long min_units = std::max<long long>(1, 2 / p.spu);
-  int grid = (int)std::min<long long>(ctas_max, std::max<long long>(1, p.units / min_units));
-  {
+  p.ytiles = items ? (int)ceil_div(M, kItemTokens) : 0;
+  p.m0 = 0;
+  int grid;
+  if (items) {
+    // one CTA per SM walks the (weight tile, token tile) items; nothing is exchanged between CTAs
+    grid = (int)std::min<long long>(sm_count(), (long long)p.tiles * p.ytiles);
+  } else {
+    // Work split.  Stream-K (equal shares of the tile x K-slot units) keeps every SM streaming, but a tile shared by
+    // several CTAs costs a partial-tile exchange through L2 at the end of the kernel, worth a few slots of
+    // streaming.  When handing out whole tiles costs fewer slots per CTA than that, each CTA gets whole tiles and
+    // nothing is exchanged.  Every CTA should stream at least two slots, or its fixed cost dominates.
+    const int occ = (wbits == 4 && ncols <= 48) ? 2 : 1;  // Cfg::kOcc
+    const long long ctas_max = std::min<long long>((long long)occ * sm_count(), kLimbMaxCtas);
+    const long long min_units = std::max<long long>(1, 2 / p.spu);
+    grid = (int)std::min<long long>(ctas_max, std::max<long long>(1, p.units / min_units));
     const long long sk_slots = ceil_div(p.units, grid) * p.spu;                 // slots per CTA, stream-K
     const long long per_sm = occ;                                               // CTAs that share an SM's bandwidth
     const long long dp_rounds = ceil_div(p.tiles, ctas_max);

@@ -40,7 +40,7 @@ def quantized_matmul_int8(x, w, scalar, zero_point=None, quant_block_size=None,
     if quantize_activation:
       return _qm._w8a8(x2, w, s32, None, x.dtype)
     out = torch.empty((M, N), dtype=x.dtype, device=x.device)
-    ws, ws_bytes = _capi.workspace(x.device, M, K) if M <= 64 else (None, 0)
+    ws, ws_bytes = _capi.workspace(x.device, M, K)
     _capi.check(_capi.lib().qmm_weight_only(
         8, _capi.ptr(x2), _capi.dtype_code(x2.dtype), _capi.ptr(w), _capi.ptr(s32), None, _capi.ptr(out),
         _capi.dtype_code(x.dtype), M, N, K, 0, _capi.VARIANTS[_qm.current_variant()], ws, ws_bytes,

@@ -272,7 +272,7 @@ def quantized_matmul_cuda(x, w, scaler, zero_point=None, block_size=-1, int4_wei
     args = (x2.data_ptr(), _capi.dtype_code(x2.dtype), w.data_ptr(), scaler32.data_ptr(),
             None if zp_after else _capi.ptr(zp32), out.data_ptr(), _capi.dtype_code(kdt), M, N, K)
     if block_size == -1:
-      ws, ws_bytes = _capi.workspace(x.device, M, K) if M <= 64 else (None, 0)
+      ws, ws_bytes = _capi.workspace(x.device, M, K)
       _capi.check(L.qmm_weight_only(8, *args, 0, _capi.VARIANTS[current_variant()], ws, ws_bytes, _capi.stream_ptr(x.device)))
     else:
       _capi.check(L.qmm_blockwise_sbn(*args, block_size, _capi.VARIANTS[current_variant()], _capi.stream_ptr(x.device)))
