@@ -150,22 +150,54 @@ class TPMlp:
       except Exception as e:  # no peer access between these GPUs: NCCL serves every batch
         print(f"[bench] peer-memory exchange unavailable ({type(e).__name__}: {e})", file=sys.stderr)
     self._i = 0
+    self.chosen = {}
 
   def lin(self, x, w, s, out_dtype=torch.bfloat16, out=None):
     from xla_b200 import packed
     return packed.quantized_matmul_packed(x, w, s, block_size=BS, int4_weight=True, weight_is_packed=True, out_dtype=out_dtype,
                                           out=out)
 
-  def exchange_for(self, m):
-    """The default sum exchange per batch: inside the decode kernel up to 8 tokens, the one-shot peer-memory kernel
-    while the partial result stays below 1 MB, NCCL above."""
+  def exchange_options(self, m):
+    """The sum exchanges that can serve a batch of m tokens on this set-up."""
     if self.world == 1:
-      return "none"
+      return ["none"]
+    opts = ["nccl"]
+    if self.peers is not None and self.peers.fits(m, H):
+      opts.append("peer")
     if self.fused is not None and self.fused.fits(m, H):
-      return "fused"
-    if self.peers is not None and self.peers.fits(m, H) and m * H * 4 < (1 << 20):
-      return "peer"
-    return "nccl"
+      opts.append("fused")
+    return opts
+
+  def exchange_for(self, m):
+    """The exchange used for a batch of m tokens: the fastest of the available forms as measured by choose_exchanges()
+    (NCCL until then)."""
+    return self.chosen.get(m, "none" if self.world == 1 else "nccl")
+
+  def choose_exchanges(self, stream, ms):
+    """Times one MLP pass per available exchange form and batch size (CUDA-graph replays, max over ranks) and keeps
+    the fastest; every rank sees the same numbers, so every rank makes the same choice."""
+    import torch.distributed as dist
+    table = {}
+    for m in ms:
+      if m not in self.x:
+        self.x[m] = self.x[64][:m].contiguous()
+      row = {}
+      for ex in self.exchange_options(m):
+        if ex == "none":
+          continue
+        try:
+          us = time_graph(lambda i: self.forward(m, exchange=ex), stream, reps=4, iters=3)
+        except Exception as e:
+          torch.cuda.synchronize(self.dev)
+          print(f"[bench] exchange {ex} at M={m} not measured ({type(e).__name__}: {e})", file=sys.stderr)
+          us = float("inf")
+        t = torch.tensor([us], dtype=torch.float64, device=self.dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        row[ex] = float(t.item())
+      if row:
+        self.chosen[m] = min(row, key=row.get)
+        table[f"M{m}"] = {k: (v if v != float("inf") else "not measured") for k, v in row.items()}
+    return table
 
   def forward(self, m, x=None, exchange=None, events=None):
     """One MLP pass on the next weight copy; `events` collects (start, end) pairs around the three linears."""
@@ -360,9 +392,12 @@ def other_configs(dev, stream, peaks, seed):
     c2[f"M{M}"] = {"us": us, "gb_per_s": byt / us / 1e3, "frac_of_hbm_peak": byt / us / 1e3 / hbm, "algorithmic_bytes": byt,
                    "kernel": _variant_name(4, M, N, K, bs)}
   # a plain read of one weight copy, launched back to back the same way: what a kernel of this size can reach at all
-  us_read = time_graph(lambda i: wp[i % copies].view(torch.int32).sum(), stream, reps=20)
+  sink = torch.zeros(1, dtype=torch.int32, device=dev)
+  Lq = _capi.lib()
+  us_read = time_graph(lambda i: _capi.check(Lq.qmm_stream_read(wp[i % copies].data_ptr(), N * K // 2, sink.data_ptr(),
+                                                                _capi.stream_ptr(dev))), stream, reps=20)
   c2["streamed_read_of_the_same_weight_bytes"] = {"us": us_read, "gb_per_s": N * K // 2 / us_read / 1e3,
-                                                  "how": "torch.sum over the int32 view of one weight copy (a library reduction kernel)"}
+                                                  "how": "qmm_stream_read over one weight copy, launched back to back like the linears"}
   # the same weights through the reference's own call: torch.ops.xla.quantized_matmul on the [S, bs, N] layout
   w_sbn = [xla_b200.unpack_int4(wp[i]).reshape(N, S, bs).permute(1, 2, 0).contiguous() for i in range(4)]
   for M in (1, 8, 32):
@@ -485,8 +520,11 @@ def run_ours(args, rank, world, local_rank):
     wl = TPMlp(dev, rank, world, args.seed)
     checked = wl.check()
     barrier()
+    exchange_table = wl.choose_exchanges(stream, (1, 8, 64, 512)) if world > 1 else None
+    barrier()
     # M = 1 and 64: one CUDA graph of `reps` passes each (eager launches if the exchange refuses capture)
     graphs, how = {}, {}
+    gph = None
     for m in MS:
       for _ in range(3):
         wl.forward(m)
@@ -568,25 +606,7 @@ def run_ours(args, rank, world, local_rank):
     extras = {}
     if not args.headline_only:
       if world > 1:
-        var = {}
-        for m in (1, 8, 64, 512):
-          if m not in wl.x:
-            wl.x[m] = wl.x[64][:m].contiguous()
-          row = {}
-          for ex in ("nccl", "peer", "fused"):
-            if (ex == "fused" and (wl.fused is None or not wl.fused.fits(m, H))) or (
-                ex == "peer" and (wl.peers is None or not wl.peers.fits(m, H))):
-              continue
-            try:
-              us = time_graph(lambda i: wl.forward(m, exchange=ex), stream, reps=4, iters=3)
-              t = torch.tensor([us], dtype=torch.float64, device=dev)
-              dist.all_reduce(t, op=dist.ReduceOp.MAX)
-              row[ex] = float(t.item())
-            except Exception as e:
-              torch.cuda.synchronize(dev)
-              row[ex] = f"not measured ({type(e).__name__})"
-          var[f"M{m}"] = row
-        extras["tp_exchange_us_per_mlp"] = var
+        extras["tp_exchange_us_per_mlp"] = exchange_table
       else:
         extras["other_configs"] = other_configs(dev, stream, peaks, args.seed)
 
@@ -641,6 +661,12 @@ def run_ours(args, rank, world, local_rank):
     if not args.no_cpu_baseline and world == 1:
       line["cpu_baseline"] = cpu_sample(args.seed)
     print(json.dumps(line), flush=True)
+  # captured graphs hold the communicator and the peer buffers: they go first
+  graphs.clear()
+  del gph
+  import gc
+  gc.collect()
+  torch.cuda.synchronize(dev)
   wl.close()
   if world > 1:
     dist.destroy_process_group()

@@ -364,6 +364,13 @@ QMM_API int qmm_device_error_flag(uint32_t* flag, void* stream);
  */
 QMM_API int qmm_set_peer_wait_limit(double seconds);
 
+/*
+ * Measurement aid: reads `bytes` of device memory at `p` (16-byte aligned) once with streaming loads and discards them;
+ * `sink` is 4 bytes of device memory.  The time of this kernel is what a decode linear whose weights are those bytes
+ * could reach at best on the same launch path.  No counterpart in the reference.
+ */
+QMM_API int qmm_stream_read(const void* p, size_t bytes, void* sink, void* stream);
+
 /* Name of the kernel family the AUTO heuristic picks (static string, for logs and tests). */
 QMM_API const char* qmm_variant_for(int op, int64_t M, int64_t N, int64_t K, int64_t block_size,
                             int has_zp);

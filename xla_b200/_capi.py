@@ -60,6 +60,7 @@ SIGNATURES = {
     "qmm_unpack_int4_nk": (_i, [_p, _p, _i64, _i64, _p]),
     "qmm_device_error_flag": (_i, [_p, _p]),
     "qmm_set_peer_wait_limit": (_i, [ctypes.c_double]),
+    "qmm_stream_read": (_i, [_p, _sz, _p, _p]),
     "qmm_variant_for": (ctypes.c_char_p, [_i, _i64, _i64, _i64, _i64, _i]),
 }
 

@@ -623,6 +623,10 @@ int qmm_device_error_flag(uint32_t* flag, void* stream) {
   return QMM_OK;
 }
 
+int qmm_stream_read(const void* p, size_t bytes, void* sink, void* stream) {
+  return launch_stream_read(p, bytes, sink, as_stream(stream));
+}
+
 int qmm_set_peer_wait_limit(double seconds) {
   if (!(seconds > 0.0) || seconds > 60.0) return fail(QMM_ERR_BAD_SHAPE, "peer wait limit must be in (0, 60] seconds, got %g", seconds);
   g_peer_wait_cycles.store((long long)(seconds * 2.0e9), std::memory_order_relaxed);  // ~2 GHz SM clock

@@ -3,6 +3,8 @@
 // zero points on large batches) so that the operator never needs a CPU fallback.
 //
 // Semantics follow torch_xla/experimental/xla_quantized_matmul.py:139-183.
+#include <algorithm>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -152,6 +154,27 @@ int launch_generic_sbn(const void* x, int x_dt, const int8_t* w, const float* sc
   dim3 grid((unsigned)ceil_div(N, 128), (unsigned)(M < 65535 ? M : 65535));
   generic_sbn_kernel<<<grid, 128, 0, st>>>(x, x_dt, w, scale, zp, out, out_dt, M, N, K, block_size);
   return check_launch("generic_sbn_kernel");
+}
+
+// A plain streaming read (16-byte loads that bypass L1, XOR-folded so that nothing is optimised away): the time a
+// kernel that only has to touch these bytes once needs, for comparison with the decode kernels.
+__global__ void __launch_bounds__(256) stream_read_kernel(const uint4* __restrict__ p, size_t n16, uint32_t* __restrict__ sink) {
+  uint32_t acc = 0;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x) {
+    const uint4 v = ld_stream_u4(p + i);
+    acc ^= v.x ^ v.y ^ v.z ^ v.w;
+  }
+  if (acc == 0x9E3779B9u) sink[0] = acc;  // practically never: keeps the loads alive
+}
+
+int launch_stream_read(const void* p, size_t bytes, void* sink, cudaStream_t st) {
+  if (!p || !sink) return fail(QMM_ERR_NULL, "stream_read: null pointer");
+  if (!aligned(p, 16)) return fail(QMM_ERR_MISALIGNED, "stream_read: the buffer must be 16-byte aligned");
+  const size_t n16 = bytes / 16;
+  if (n16 == 0) return QMM_OK;
+  const int blocks = (int)std::min<size_t>((size_t)sm_count() * 8, (n16 + 255) / 256);
+  stream_read_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const uint4*>(p), n16, reinterpret_cast<uint32_t*>(sink));
+  return check_launch("stream_read_kernel");
 }
 
 int launch_generic_w8a8(const int8_t* xq, const int8_t* w, const float* w_scale, const float* zp,

@@ -27,6 +27,8 @@ int launch_generic_w8a8(const int8_t* xq, const int8_t* w, const float* w_scale,
                         const float* x_scale, const int32_t* rowsum, int32_t* acc_out, void* out,
                         int out_dt, int64_t M, int64_t N, int64_t K, cudaStream_t st);
 
+int launch_stream_read(const void* p, size_t bytes, void* sink, cudaStream_t st);
+
 // ---- gemv.cu ------------------------------------------------------------------------------
 // Decode kernels for weights stored [N,K] (int8) or [N,K/2] (packed int4).  block_size == 0
 // means per-channel scales.  Returns QMM_ERR_UNSUPPORTED / QMM_ERR_MISALIGNED when the shape
