@@ -18,7 +18,7 @@
 // integer instructions per eight weights instead of the nine-plus-four of an int4 -> bf16 conversion); the factor
 // 16 is folded into the per-token power of two.
 //
-// Structure.  "Swap-AB": 128 weight rows are the MMA's M side, the limb columns (3 per token, 16..192) its N side.
+// Structure.  "Swap-AB": 128 weight rows are the MMA's M side, the limb columns (3 per token, 16..128) its N side.
 //   split_rows_kernel   one CTA per token: row maximum, limbs (in the k order the weight operand uses), 2^(e-21)
 //   limb_tc_kernel      one CTA per SM, stream-K: the (row tile, 256-value K slot) units are dealt to the CTAs in
 //                       equal contiguous shares, so every SM streams the same number of weight bytes whatever N and
@@ -871,7 +871,6 @@ int ncols_for(int64_t M) {
   if (M <= 10) return 32;
   if (M <= 16) return 48;
   if (M <= 32) return 96;
-  if (M <= 64) return 192;
   return 128;  // larger batches: token tiles of 42 (126 limb columns), see launch_limb_tc
 }
 
@@ -891,7 +890,7 @@ Scratch carve(void* base, int64_t M, int64_t K, int max_ctas) {
   s.limbs = reinterpret_cast<int8_t*>(b + off);
   off += align_up((size_t)3 * M * K, 256);
   s.partial = reinterpret_cast<float*>(b + off);
-  if (M <= 64) off += (size_t)max_ctas * (ncols_for(M) / 3) * BMW * 4;  // item mode exchanges nothing
+  if (ncols_for(M) != 128) off += (size_t)max_ctas * (ncols_for(M) / 3) * BMW * 4;  // item mode exchanges nothing
   s.bytes = off;
   return s;
 }
@@ -933,8 +932,7 @@ int launch_ncols(int ncols, const CUtensorMap& map_w, const CUtensorMap& map_x, 
     case 32: return launch_cfg<WBITS, 32>(map_w, map_x, p, grid, st);
     case 48: return launch_cfg<WBITS, 48>(map_w, map_x, p, grid, st);
     case 96: return launch_cfg<WBITS, 96>(map_w, map_x, p, grid, st);
-    case 128: return launch_cfg<WBITS, 128>(map_w, map_x, p, grid, st);
-    default: return launch_cfg<WBITS, 192>(map_w, map_x, p, grid, st);
+    default: return launch_cfg<WBITS, 128>(map_w, map_x, p, grid, st);
   }
 }
 
@@ -1022,7 +1020,7 @@ int launch_limb_tc(int wbits, const void* x, int x_dt, const void* w, const floa
   }
   const Scratch sc = carve(workspace, M, K, kLimbMaxCtas);
   const int ncols = ncols_for(M);
-  const bool items = M > 64;
+  const bool items = ncols == 128;
 
   Params p;
   p.scale = scale;
