@@ -38,7 +38,7 @@ def _run(x, w_nk, s, bs, wbits, out_dtype):
                    weight_is_packed=wbits == 4, out_dtype=out_dtype)
 
 
-# every token-count class of the kernel (limb columns 16, 32, 48, 96, 192) and both edges of each
+# every token-count class of the kernel (limb columns 16, 32, 48, 96, one and two 42-token tiles) and the edges of each
 @pytest.mark.parametrize("M", [1, 2, 5, 6, 10, 11, 16, 17, 32, 33, 42, 43, 64])
 @pytest.mark.parametrize("wbits,bs", [(8, 0), (8, 128), (4, 128), (4, 0)])
 def test_token_classes(M, wbits, bs):
