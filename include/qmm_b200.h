@@ -138,20 +138,26 @@ QMM_API int qmm_w8a16_blockwise(const void* x, int x_dtype, const int8_t* w, con
 
 /*
  * Any of the four weight-only linears above on K-minor weights, with caller scratch: the one entry point that can
- * run QMM_VARIANT_I8TC, which QMM_VARIANT_AUTO prefers for 1 <= M <= 64 when it applies and the workspace suffices
- * (otherwise AUTO chooses as the entry points above do, and the workspace is not touched).
+ * run QMM_VARIANT_I8TC, which QMM_VARIANT_AUTO picks where the measured table or its shape rule names it and the
+ * workspace suffices (otherwise AUTO chooses as the entry points above do, and the workspace is not touched).
  *   wbits 8: w int8 [N,K];  wbits 4: w uint8 [N,K/2], nibble order as qmm_w4a16_blockwise_packed.
  *   block_size <= 0: per-channel, scale/zp f32 [N];  block_size > 0: scale/zp f32 [K/block_size, N].
  *   workspace: qmm_weight_only_workspace_size(max M, K) bytes of device memory, 256-byte aligned, whose first
  *   1024 bytes are ZERO before the first call (the kernel leaves them zero); calls that share a workspace must be
- *   ordered on the GPU (same stream).  NULL / 0 is allowed and rules the I8TC variant out.
+ *   ordered on the GPU (same stream).  NULL / 0 is allowed and rules the I8TC variant out.  A workspace of
+ *   qmm_weight_only_workspace_size_for(wbits, max M, N, K) bytes additionally lets long int4 batches (384 tokens
+ *   and more per channel, 768 with scale blocks) expand the weights to int8 once per call (N*K bytes behind the
+ *   regular scratch; with less room they are expanded in slices of rows, or per tile inside the kernel as for short
+ *   batches): 1.2x faster at 512 tokens per channel, 1.1-1.3x at 1024.  Results are bit-identical either way.
  * I8TC computes  sum_k X[m,k] * w[n,k]  exactly in int32, where X is the activation row in 22-bit fixed point
  * relative to the row's largest exponent (exact for bf16/f16 values within 2^-14 of the row maximum, rounded at
- * 2^-22 of it below), then applies scales in fp32: the accuracy of an fp32 accumulation.
+ * 2^-22 of it below), then applies scales in fp32: the accuracy of an fp32 accumulation.  (16-bit outputs above 32
+ * tokens: 15-bit fixed point, see qmm_set_activation_limbs.)
  * Replaces: torch.ops.xla.quantized_matmul without activation quantization
  *   (torch_xla/experimental/xla_quantized_matmul.py:101-124 XLA key, :152-170 CPU key).
  */
 QMM_API size_t qmm_weight_only_workspace_size(int64_t max_M, int64_t K);
+QMM_API size_t qmm_weight_only_workspace_size_for(int wbits, int64_t max_M, int64_t N, int64_t K);
 /*
  * The kernel family the measured table names for a shape (a QMM_VARIANT_* value), or 0 when the table has no entry
  * and QMM_VARIANT_AUTO falls back to its shape rule.  The table is generated on a B200 by `python -m xla_b200.tune`
@@ -180,6 +186,15 @@ QMM_API int qmm_weight_only(int wbits, const void* x, int x_dtype, const void* w
  */
 QMM_API int qmm_gate_up_decode(int wbits, const void* x, int x_dtype, const void* w, const float* scale, void* out,
                        int out_dtype, int64_t M, int64_t N2, int64_t K, int64_t block_size, void* stream);
+/*
+ * The same fused operation for any batch up to 1008 tokens on the split-activation kernel (QMM_VARIANT_I8TC), whose
+ * drain warps apply silu(gate) * up before the one store: bf16 / f16 / f32 activations, K >= 128 and a multiple of
+ * 16 (int8) or 32 (int4), block_size 0, 128 or a multiple of 256.  workspace: as for qmm_weight_only
+ * (qmm_weight_only_workspace_size(M, K) bytes, 256-byte aligned, first 1024 bytes zero before the first use).
+ * Returns QMM_ERR_UNSUPPORTED outside that range.  No counterpart in the reference (see qmm_gate_up_decode).
+ */
+QMM_API int qmm_gate_up(int wbits, const void* x, int x_dtype, const void* w, const float* scale, void* out, int out_dtype,
+                int64_t M, int64_t N2, int64_t K, int64_t block_size, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * Per-token dynamic activation quantizer:
@@ -353,6 +368,19 @@ QMM_API int qmm_host_pipeline_destroy(void* pipeline);
  * clears it.  Returns QMM_ERR_TIMEOUT if it was non-zero.
  */
 QMM_API int qmm_device_error_flag(uint32_t* flag, void* stream);
+
+/*
+ * Precision of the split-activation kernel (QMM_VARIANT_I8TC) above 32 tokens.  It rewrites every activation row as
+ * fixed point below the row's largest value and multiplies int8 "limbs" of it with the integer weights exactly.
+ * Three limbs (22 bits) give the accuracy of an fp32 accumulation and are used for fp32 outputs and for every batch
+ * of up to 32 tokens.  limbs = 0 (default): bf16 / f16 outputs above 32 tokens use two limbs, i.e. each activation
+ * carries an error of at most 2^-15 of its row's largest |x| - ~1e-4 of the output's scale for N(0,1) rows, ~1e-3
+ * when 1 % of the entries are 20 times larger, under the 2^-9 rounding of a bf16 output; a third fewer tensor-core
+ * columns per token.  limbs = 3: three limbs everywhere.  Process-wide; applies to launches made after the call.
+ * The reference multiplies bf16 activations with the up-cast weights in bf16 x bf16 -> fp32
+ * (torch_xla/experimental/xla_quantized_matmul.py:113-114, :120-124); it has no such knob.
+ */
+QMM_API int qmm_set_activation_limbs(int limbs);
 
 /*
  * How long the kernels that wait for another GPU (qmm_allreduce_oneshot, qmm_rowparallel_decode) keep waiting

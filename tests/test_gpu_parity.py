@@ -601,6 +601,39 @@ def test_gate_up_fused(M, mode):
     assert qo.max_abs_rel(out16, _silu_mul(gate, up)) < TOL_BF16
 
 
+@pytest.mark.parametrize("M", [33, 64, 100, 600])
+@pytest.mark.parametrize("mode", ["w4_blockwise", "w8_per_channel"])
+def test_gate_up_fused_large_batches(M, mode):
+  """Above 32 tokens the split-activation kernel applies silu(gate) * up in its drain: one launch, no [M, 2N] round trip."""
+  g = qc.gen(44)
+  N, K, bs = 1000 - 1000 % 8, 1024, 128
+  x = qc.activations(g, M, K)
+  if mode == "w4_blockwise":
+    wg, wu = qc.int4_weight(g, N, K), qc.int4_weight(g, N, K)
+    sg, su = qc.blockwise_scale(g, K // bs, N), qc.blockwise_scale(g, K // bs, N)
+    gate = qo.quantized_matmul(x.float(), qc.to_sbn(wg, bs), sg, block_size=bs, dot_round=None)
+    up = qo.quantized_matmul(x.float(), qc.to_sbn(wu, bs), su, block_size=bs, dot_round=None)
+    w, s = xla_b200.interleave_gate_up(xla_b200.pack_int4(cu(wg)), xla_b200.pack_int4(cu(wu)), cu(sg), cu(su), bs)
+    kw = dict(block_size=bs, int4_weight=True, weight_is_packed=True)
+  else:
+    wg, wu = qc.int8_weight(g, N, K), qc.int8_weight(g, N, K)
+    sg, su = qc.per_channel_scale(g, N), qc.per_channel_scale(g, N)
+    gate = qo.quantized_matmul(x, wg, sg, dot_round=None)
+    up = qo.quantized_matmul(x, wu, su, dot_round=None)
+    w, s = xla_b200.interleave_gate_up(cu(wg), cu(wu), cu(sg), cu(su))
+    kw = {}
+  want = _silu_mul(gate, up)
+  out = torch.ops.xla_b200.quantized_gate_up(cu(x), w, s, **kw)
+  assert out.shape == (M, N) and out.dtype == torch.float32
+  assert qo.max_abs_rel(out, want) < TOL_F32
+  out16 = torch.ops.xla_b200.quantized_gate_up(cu(x), w, s, out_dtype=torch.bfloat16, **kw)
+  assert out16.dtype == torch.bfloat16
+  assert qo.max_abs_rel(out16, want) < TOL_BF16
+  with xla_b200.force_variant("tcgen05"):  # the stacked-linear route computes the same thing
+    ref = torch.ops.xla_b200.quantized_gate_up(cu(x), w, s, **kw)
+  assert qo.max_abs_rel(out, ref.cpu()) < TOL_F32
+
+
 def test_concat_projections_qkv():
   """q, k, v read the same activations: one weight stream, outputs split afterwards."""
   g = qc.gen(41)
@@ -655,6 +688,34 @@ def test_reference_style_module_variants(n_bits, block_size, symmetric, qa):
   ref = qo.quantized_matmul(x, m.weight.cpu(), m.weight_scaler.cpu(), None if m.zero_point is None else m.zero_point.cpu(),
                             block_size=block_size, quantize_activation=qa)
   assert qo.max_abs_rel(out_q, ref) < 1e-4
+
+
+def test_torch_compile_default_backend():
+  """The module and the two sibling operators under torch.compile with its default backend (the reference compiles
+  its module with backend="openxla", test/quantized_ops/test_quantized_matmul.py:128-143): the operators are opaque
+  custom ops with Meta kernels, so the compiled graphs call the same kernels and give the same bits."""
+  g = qc.gen(31)
+  K, N, bs = 1024, 512, 128
+  x = cu(qc.activations(g, 4, K))
+  m = xla_b200.XlaQuantizedLinear(K, N, is_symmetric=True)
+  m.load_quantized_weight(cu(qc.int8_weight(g, N, K)), cu(qc.per_channel_scale(g, N)))
+  assert torch.equal(torch.compile(m, fullgraph=True)(x), m(x))
+
+  wp = xla_b200.pack_int4(cu(qc.int4_weight(g, N, K)))
+  sb = cu(qc.blockwise_scale(g, K // bs, N))
+
+  def packed(a):
+    return torch.ops.xla_b200.quantized_matmul_packed(a, wp, sb, block_size=bs, int4_weight=True, weight_is_packed=True,
+                                                      out_dtype=torch.bfloat16) * 2.0
+  assert torch.equal(torch.compile(packed, fullgraph=True)(x), packed(x))
+
+  wgu, sgu = xla_b200.interleave_gate_up(xla_b200.pack_int4(cu(qc.int4_weight(g, N, K))), xla_b200.pack_int4(cu(qc.int4_weight(g, N, K))),
+                                         cu(qc.blockwise_scale(g, K // bs, N)), cu(qc.blockwise_scale(g, K // bs, N)), bs)
+
+  def gate_up(a):
+    return torch.ops.xla_b200.quantized_gate_up(a, wgu, sgu, block_size=bs, int4_weight=True, weight_is_packed=True)
+  for xx in (x, cu(qc.activations(g, 48, K))):
+    assert torch.equal(torch.compile(gate_up, fullgraph=True)(xx), gate_up(xx))
 
 
 def test_torch_compile_and_cuda_graph_pass_through():

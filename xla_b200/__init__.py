@@ -7,7 +7,7 @@ Importing the package registers ``torch.ops.xla.quantized_matmul``,
 """
 from . import _capi  # noqa: F401
 from .quantized_matmul import (XlaQuantizedLinear, force_variant, quantize_tensor,  # noqa: F401
-                               set_activation_saturation, set_prepack_cache)
+                               set_activation_limbs, set_activation_saturation, set_prepack_cache)
 from . import custom_kernel  # noqa: F401
 from . import packed  # noqa: F401
 from .packed import pack_int4, quantized_matmul_packed, unpack_int4  # noqa: F401
@@ -16,7 +16,7 @@ from .mlp import concat_projections, interleave_gate_up, quantized_gate_up, spli
 from .host import HostLinear, HostPipeline  # noqa: F401
 
 __all__ = [
-    "XlaQuantizedLinear", "force_variant", "quantize_tensor", "set_activation_saturation", "set_prepack_cache", "pack_int4",
+    "XlaQuantizedLinear", "force_variant", "quantize_tensor", "set_activation_limbs", "set_activation_saturation", "set_prepack_cache", "pack_int4",
     "unpack_int4", "quantized_matmul_packed", "interleave_gate_up", "quantized_gate_up", "concat_projections",
     "split_outputs", "HostPipeline", "HostLinear"
 ]

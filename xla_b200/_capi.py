@@ -30,6 +30,7 @@ SIGNATURES = {
     "qmm_w4a16_perchannel_packed": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i, _p]),
     "qmm_w8a16_blockwise": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _p]),
     "qmm_weight_only_workspace_size": (_sz, [_i64, _i64]),
+    "qmm_weight_only_workspace_size_for": (_sz, [ctypes.c_int, _i64, _i64, _i64]),
     "qmm_tuned_variant": (_i, [_i, _i64, _i64, _i64, _i64]),
     "qmm_weight_only_variant_for": (ctypes.c_char_p, [_i, _i64, _i64, _i64, _i64, _i]),
     "qmm_weight_only": (_i, [_i, _p, _i, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _p, _sz, _p]),
@@ -59,7 +60,9 @@ SIGNATURES = {
     "qmm_pack_int4_sbn": (_i, [_p, _p, _i64, _i64, _i64, _p]),
     "qmm_unpack_int4_nk": (_i, [_p, _p, _i64, _i64, _p]),
     "qmm_device_error_flag": (_i, [_p, _p]),
+    "qmm_gate_up": (_i, [ctypes.c_int, _p, ctypes.c_int, _p, _p, _p, ctypes.c_int, _i64, _i64, _i64, _i64, _p, _sz, _p]),
     "qmm_set_peer_wait_limit": (_i, [ctypes.c_double]),
+    "qmm_set_activation_limbs": (_i, [ctypes.c_int]),
     "qmm_stream_read": (_i, [_p, _sz, _p, _p]),
     "qmm_variant_for": (ctypes.c_char_p, [_i, _i64, _i64, _i64, _i64, _i]),
 }
@@ -127,11 +130,12 @@ def on_device(device, fn):
 _workspaces = {}
 
 
-def workspace(device, max_M, K):
+def workspace(device, max_M, K, N=0, wbits=8):
   """Scratch for ``qmm_weight_only`` on torch's current stream of `device`: (pointer, bytes), or (None, 0) when no
-  variant needs one.  One buffer per (device, stream), zero-filled when created (the kernels keep its flag words
+  variant needs one; with N and wbits, including the room that lets a long int4 batch expand its weights to int8
+  once.  One buffer per (device, stream), zero-filled when created (the kernels keep its flag words
   zero) and grown on demand; a stream capture in progress never allocates - it gets the existing buffer or none."""
-  need = lib().qmm_weight_only_workspace_size(max_M, K)
+  need = lib().qmm_weight_only_workspace_size_for(wbits, max_M, N, K) if N else lib().qmm_weight_only_workspace_size(max_M, K)
   if need == 0:
     return None, 0
   idx = device.index if device.index is not None else torch.cuda.current_device()

@@ -344,6 +344,12 @@ size_t qmm_weight_only_workspace_size(int64_t max_M, int64_t K) {
   return limb_tc_workspace_bytes(max_M, K);
 }
 
+size_t qmm_weight_only_workspace_size_for(int wbits, int64_t max_M, int64_t N, int64_t K) {
+  const size_t base = limb_tc_workspace_bytes(max_M, K);
+  if (base == 0 || N < 1) return base;
+  return (base + 255) / 256 * 256 + limb_tc_wide_bytes(wbits, max_M, N, K);
+}
+
 int qmm_weight_only(int wbits, const void* x, int x_dtype, const void* w, const float* scale, const float* zp, void* out,
                     int out_dtype, int64_t M, int64_t N, int64_t K, int64_t block_size, int variant, void* workspace,
                     size_t workspace_bytes, void* stream) {
@@ -404,6 +410,20 @@ int qmm_gate_up_decode(int wbits, const void* x, int x_dtype, const void* w, con
                 (long long)block_size);
   log_choice("gate_up_decode", "mma", M, N2, K);
   return launch_decode_mma(wbits, x, x_dtype, w, scale, out, out_dtype, M, N2, K, block_size, st, 1);
+}
+
+int qmm_gate_up(int wbits, const void* x, int x_dtype, const void* w, const float* scale, void* out, int out_dtype, int64_t M,
+                int64_t N2, int64_t K, int64_t block_size, void* workspace, size_t workspace_bytes, void* stream) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (wbits != 4 && wbits != 8) return fail(QMM_ERR_BAD_SHAPE, "gate_up: wbits must be 4 or 8, got %d", wbits);
+  if (!x || !w || !scale || !out) return fail(QMM_ERR_NULL, "gate_up: null pointer");
+  if (M < 0 || N2 < 0 || K < 0) return fail(QMM_ERR_BAD_SHAPE, "gate_up: negative size");
+  if (N2 % 16 != 0) return fail(QMM_ERR_BAD_SHAPE, "gate_up: N2 must be a multiple of 16, got %lld", (long long)N2);
+  if (block_size < 0 || (block_size > 0 && K % block_size != 0))
+    return fail(QMM_ERR_BAD_SHAPE, "gate_up: K (%lld) must be a multiple of block_size (%lld)", (long long)K, (long long)block_size);
+  if (M == 0 || N2 == 0) return QMM_OK;
+  log_choice("gate_up", "i8tc", M, N2, K);
+  return launch_limb_tc(wbits, x, x_dtype, w, scale, out, out_dtype, M, N2, K, block_size, 1, workspace, workspace_bytes, st);
 }
 
 int qmm_w4a16_perchannel_packed(const void* x, int x_dtype, const uint8_t* wp, const float* scale,
@@ -625,6 +645,12 @@ int qmm_device_error_flag(uint32_t* flag, void* stream) {
 
 int qmm_stream_read(const void* p, size_t bytes, void* sink, void* stream) {
   return launch_stream_read(p, bytes, sink, as_stream(stream));
+}
+
+int qmm_set_activation_limbs(int limbs) {
+  if (limbs != 0 && limbs != 3) return fail(QMM_ERR_BAD_SHAPE, "qmm_set_activation_limbs: 0 (by output type) or 3, got %d", limbs);
+  limb_tc_set_limbs(limbs);
+  return QMM_OK;
 }
 
 int qmm_set_peer_wait_limit(double seconds) {

@@ -61,6 +61,9 @@ int launch_decode_mma_allreduce(int wbits, const void* x, int x_dt, const void* 
 // kernel leaves them zero).  gate_up as in launch_decode_mma.
 constexpr int kLimbMaxCtas = 320;  // two CTAs per SM on up to 160 SMs
 size_t limb_tc_workspace_bytes(int64_t M, int64_t K);
+// extra bytes behind the regular scratch that let a long int4 batch expand its weights to int8 once (0: no use for them)
+size_t limb_tc_wide_bytes(int wbits, int64_t M, int64_t N, int64_t K);
+void limb_tc_set_limbs(int limbs);  // 3: three limbs per token everywhere; anything else: two for 16-bit outputs above 32 tokens
 bool limb_tc_shape_ok(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size, int x_dt, bool has_zp);
 bool limb_tc_supported(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size, const void* x, int x_dt,
                        const void* w, bool has_zp);

@@ -33,6 +33,7 @@
 //                       take alternate slots
 // Weight bytes in flight per SM = the depth of the TMA ring (64-190 KB), independent of registers and occupancy.
 #include <algorithm>
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 
@@ -94,7 +95,9 @@ struct Params {
   void* out;
   int out_dt;
   int M;
-  int64_t N;
+  int64_t N;   // weight rows of this launch
+  int64_t ld;  // row pitch of `out` and of the scale blocks (the whole layer's N when a launch covers a slice of rows)
+  int w_dep;   // the weight operand is written by the kernel before this one (int4 expanded to int8 first)
   int tiles;   // ceil(N / 128)
   int slots;   // K slots per tile
   int spu;     // slots per scheduling unit (= slots per scale block in kBlockSlots mode, else 1)
@@ -110,7 +113,9 @@ struct Params {
   int m0;      // first token of this launch inside the caller's batch (row offset of `out`)
 };
 
-template <int WBITS, int NCOLS>
+// NL = limbs per token: three (22-bit fixed point: fp32-accumulation accuracy), or two (15 bits relative to the row's
+// largest value: below the resolution of a 16-bit output) for the widest tiles when the output is bf16 / f16.
+template <int WBITS, int NCOLS, int NL = 3>
 struct Cfg {
   static constexpr uint32_t kBTile = NCOLS * 128;
   // CTAs per SM.  With int4 weights and up to 48 limb columns a CTA takes at most half of an SM's shared memory, tensor memory and
@@ -139,10 +144,13 @@ struct Cfg {
   static constexpr int kRegions = std::min(2 * kMaxAcc, kAccCols / NCOLS);   // accumulators that fit in TMEM
   // two accumulators of a block-128 slot share one hand-over between MMA issuer and drain warps
   static constexpr bool kPair = kRegions >= 4;
-  static constexpr int kTokens = NCOLS / 3;
+  static constexpr int kTokens = NCOLS / NL;
   // drain warps: four (one per TMEM lane quadrant), or eight for the large-batch tiles, where the two warps of a
   // quadrant take half of the tile's tokens each (the per-block rescaling is what bounds that mode)
   static constexpr int kHalves = NCOLS == 128 ? 2 : 1;
+  // tensor-memory loads of the drain double-buffered in registers: tiles of more than 16 tokens, where the register
+  // budget allows (the int4 instances of the widest tiles run 640 threads)
+  static constexpr bool kPipeDrain = NCOLS >= 96 && !(WBITS == 4 && NCOLS == 128);
   static constexpr int kXDrainWarp0 = 8 + 4 * kGroups;
   static constexpr int kThreads = 256 + 128 * kGroups + 128 * (kHalves - 1);
   static constexpr size_t kSmem = 1024 + (size_t)kRaw * kRawBytes + (size_t)kSlots * kSlot + 1024;
@@ -203,7 +211,6 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void drain_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 __device__ __forceinline__ float silu_mul(float gate, float up) { return gate / (1.f + expf(-gate)) * up; }
 __device__ __forceinline__ int64_t gate_up_column(int64_t n) { return ((n >> 4) << 3) + (n & 7); }
@@ -241,14 +248,18 @@ __device__ __forceinline__ void load8<__half>(const __half* p, float* v) {
   }
 }
 
-// 2^(21-e) and 2^(e-21) * pw_mul for a row whose largest |x| has the float bits `mx`; a row with a non-finite entry
-// gets (0, NaN), an all-zero or denormal row any small exponent.
+// 2^(q-e) and 2^(e-q) * pw_mul for a row whose largest |x| has the float bits `mx`; a row with a non-finite entry
+// gets (0, NaN), an all-zero or denormal row any small exponent.  Three limbs: q = 21 (|X| < 2^22 of the 2^23 that
+// balanced limbs hold).  Two limbs: balanced limbs hold -32896..32639, so q = 14 unless the row's largest value
+// would round above 32639 (mantissa beyond 32639 / 16384), which takes q = 13.
+template <int NL>
 __device__ __forceinline__ void row_factors(uint32_t mx, float pw_mul, float& mult, float& pw) {
   int e = (int)(mx >> 23) - 127;
   const bool finite = e < 128;
   if (e < -100) e = -100;
-  mult = finite ? __uint_as_float((uint32_t)(21 - e + 127) << 23) : 0.f;
-  pw = finite ? __uint_as_float((uint32_t)(e - 21 + 127) << 23) * pw_mul : __uint_as_float(0x7fc00000u);
+  const int q = NL == 3 ? 21 : ((mx & 0x7fffffu) > 0x7EFE00u ? 13 : 14);
+  mult = finite ? __uint_as_float((uint32_t)(q - e + 127) << 23) : 0.f;
+  pw = finite ? __uint_as_float((uint32_t)(e - q + 127) << 23) * pw_mul : __uint_as_float(0x7fc00000u);
 }
 
 // Eight values -> the bytes of their three limbs, packed in k order (two words per limb).
@@ -256,27 +267,32 @@ __device__ __forceinline__ void row_factors(uint32_t mx, float pw_mul, float& mu
 // round-to-nearest-even IS the rint, and X sits in the low mantissa bits).  Balanced limbs l_i in [-128,127] with
 // X = l0 + 256 l1 + 65536 l2 are the base-256 digits of X + 0x808080, each minus 128: one integer add puts the digits
 // into bytes 0..2, one XOR with 0x808080 turns digit into limb.  Three instructions per value, then byte gathers.
+// With two limbs the same holds for X + 0x8080 and bytes 0..1 (l2 is not written).
+template <int NL>
 __device__ __forceinline__ void split8(const float* v, float mult, uint32_t* l0, uint32_t* l1, uint32_t* l2) {
+  constexpr uint32_t kBias = NL == 3 ? 0x808080u : 0x8080u;
   uint32_t z[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i)
-    z[i] = (__float_as_uint(fmaf(v[i], mult, 12582912.f)) + (0x808080u - 0x4B400000u)) ^ 0x808080u;
+    z[i] = (__float_as_uint(fmaf(v[i], mult, 12582912.f)) + (kBias - 0x4B400000u)) ^ kBias;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const uint32_t a = z[4 * h], b = z[4 * h + 1], c = z[4 * h + 2], d = z[4 * h + 3];
     // byte j of a/b in the low half, of c/d in the high half
     const uint32_t ab0 = __byte_perm(a, b, 0x0040), cd0 = __byte_perm(c, d, 0x0040);
     const uint32_t ab1 = __byte_perm(a, b, 0x0051), cd1 = __byte_perm(c, d, 0x0051);
-    const uint32_t ab2 = __byte_perm(a, b, 0x0062), cd2 = __byte_perm(c, d, 0x0062);
     l0[h] = __byte_perm(ab0, cd0, 0x5410);
     l1[h] = __byte_perm(ab1, cd1, 0x5410);
-    l2[h] = __byte_perm(ab2, cd2, 0x5410);
+    if constexpr (NL == 3) {
+      const uint32_t ab2 = __byte_perm(a, b, 0x0062), cd2 = __byte_perm(c, d, 0x0062);
+      l2[h] = __byte_perm(ab2, cd2, 0x5410);
+    }
   }
 }
 
-// One CTA per token row.  xl: [3*M][K] int8, row 3*m + l = limb l of token m; pw[m] = 2^(e_m - 21) * pw_mul.
+// One CTA per token row.  xl: [NL*M][K] int8, row NL*m + l = limb l of token m; pw[m] = 2^(e_m - q) * pw_mul.
 // A row with a non-finite entry gets pw = NaN (its outputs are NaN); an all-zero row gets zeros.
-template <typename XT>
+template <typename XT, int NL>
 __global__ void __launch_bounds__(1024) split_rows_kernel(const XT* __restrict__ x, int8_t* __restrict__ xl, float* __restrict__ pw,
                                                           int64_t K, int perm4, float pw_mul) {
   __shared__ uint32_t s_max[32];
@@ -307,21 +323,21 @@ __global__ void __launch_bounds__(1024) split_rows_kernel(const XT* __restrict__
   __syncthreads();
   mx = s_max[0];
   float mult, pwv;
-  row_factors(mx, pw_mul, mult, pwv);
+  row_factors<NL>(mx, pw_mul, mult, pwv);
   if (threadIdx.x == 0) pw[m] = pwv;
-  int8_t* r0 = xl + (int64_t)(3 * m) * K;
+  int8_t* r0 = xl + (int64_t)(NL * m) * K;
   int8_t* r1 = r0 + K;
   int8_t* r2 = r1 + K;
   for (int64_t gi = threadIdx.x; gi < groups; gi += blockDim.x) {
     float v[8];
     load8<XT>(xr + gi * 8, v);
-    uint32_t l0[2], l1[2], l2[2];  // bytes of limb l for k = 8*gi + i, packed in k order
-    split8(v, mult, l0, l1, l2);
+    uint32_t l0[2], l1[2], l2[2] = {0u, 0u};  // bytes of limb l for k = 8*gi + i, packed in k order
+    split8<NL>(v, mult, l0, l1, l2);
     if (!perm4) {
       const int64_t o = gi * 8;
       *reinterpret_cast<uint2*>(r0 + o) = make_uint2(l0[0], l0[1]);
       *reinterpret_cast<uint2*>(r1 + o) = make_uint2(l1[0], l1[1]);
-      *reinterpret_cast<uint2*>(r2 + o) = make_uint2(l2[0], l2[1]);
+      if constexpr (NL == 3) *reinterpret_cast<uint2*>(r2 + o) = make_uint2(l2[0], l2[1]);
     } else {
       // k = 32*c + 8*j + i -> even i at 32*c + 4*j + i/2, odd i at 32*c + 16 + 4*j + i/2
       const int64_t base = (gi >> 2) * 32 + (gi & 3) * 4;
@@ -331,26 +347,64 @@ __global__ void __launch_bounds__(1024) split_rows_kernel(const XT* __restrict__
       *reinterpret_cast<uint32_t*>(r0 + base + 16) = odds(l0);
       *reinterpret_cast<uint32_t*>(r1 + base) = evens(l1);
       *reinterpret_cast<uint32_t*>(r1 + base + 16) = odds(l1);
-      *reinterpret_cast<uint32_t*>(r2 + base) = evens(l2);
-      *reinterpret_cast<uint32_t*>(r2 + base + 16) = odds(l2);
+      if constexpr (NL == 3) {
+        *reinterpret_cast<uint32_t*>(r2 + base) = evens(l2);
+        *reinterpret_cast<uint32_t*>(r2 + base + 16) = odds(l2);
+      }
     }
   }
   if (blockIdx.x == 0 && threadIdx.x == 0) { DBG_STAMP(12); }
+}
+
+// ---- int4 -> int8 once, for long batches ----
+// Packed nibbles [rows, K/2] -> int8 [rows, K] holding value * 16 in natural k order.  Above a couple of hundred tokens
+// the per-tile expansion inside the main kernel costs more than this pass over the weights (read N*K/2, write N*K
+// bytes at HBM rate) plus the int8 kernel, which runs at more than twice the rate.  Thread = 8 packed bytes at a time
+// (loads and 16-byte stores of a warp are contiguous).
+__global__ void __launch_bounds__(256) expand_int4_kernel(const uint2* __restrict__ src, uint4* __restrict__ dst, int64_t chunks) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  constexpr int U = 4;  // loads in flight per thread
+  uint2 q[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) q[u] = i + u * stride < chunks ? __ldcs(src + i + u * stride) : make_uint2(0, 0);
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // `dst` may still be read by the kernel before this one
+  while (i < chunks) {
+    uint2 qn[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t nx = i + (U + u) * stride;
+      qn[u] = nx < chunks ? __ldcs(src + nx) : make_uint2(0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (i + u * stride < chunks) {
+        const uint32_t lo0 = (q[u].x << 4) & 0xF0F0F0F0u, hi0 = q[u].x & 0xF0F0F0F0u;  // even k, odd k
+        const uint32_t lo1 = (q[u].y << 4) & 0xF0F0F0F0u, hi1 = q[u].y & 0xF0F0F0F0u;
+        dst[i + u * stride] = make_uint4(__byte_perm(lo0, hi0, 0x5140), __byte_perm(lo0, hi0, 0x7362),
+                                         __byte_perm(lo1, hi1, 0x5140), __byte_perm(lo1, hi1, 0x7362));
+      }
+      q[u] = qn[u];
+    }
+    i += U * stride;
+  }
 }
 
 // ---- the stream-K tensor-core kernel -----------------------------------------------------------------------------
 // One accumulator (NCOLS int32 columns of this thread's TMEM lane) -> limbs recombined in fp32, times sc, into total.
 // SMALL: every int32 sum is below 2^22 in magnitude (scale blocks of at most 256 values), so 256 * A1 + A0 still fits
 // an int32 and one conversion serves both low limbs.
-template <int NCOLS, int MT, bool SMALL, typename Release>
+template <int NCOLS, int MT, int NL, bool SMALL, typename Release>
 __device__ __forceinline__ void fold_region(uint32_t taddr, float sc, float (&total)[MT], bool release_after, Release release) {
-  constexpr int kChunks = (NCOLS + 47) / 48;
+  constexpr int CW = 16 * NL;  // columns of a chunk of 16 tokens
+  constexpr int kChunks = (NCOLS + CW - 1) / CW;
 #pragma unroll
   for (int c = 0; c < kChunks; ++c) {
-    uint32_t r[48];
+    uint32_t r[CW];
 #pragma unroll
-    for (int j = 0; j < 3; ++j)
-      if (c * 48 + 16 * j < NCOLS) ptx::tmem_ld_32x32b_x16(taddr + c * 48 + 16 * j, r + 16 * j);
+    for (int j = 0; j < NL; ++j)
+      if (c * CW + 16 * j < NCOLS) ptx::tmem_ld_32x32b_x16(taddr + c * CW + 16 * j, r + 16 * j);
     ptx::tmem_ld_wait();
     if (c == kChunks - 1 && release_after) release();  // the accumulator's last values are in registers
 #pragma unroll
@@ -358,20 +412,87 @@ __device__ __forceinline__ void fold_region(uint32_t taddr, float sc, float (&to
       if (c * 16 + t < MT) {
         float lowf;
         if (SMALL) {
-          lowf = __int2float_rn((int)r[3 * t + 1] * 256 + (int)r[3 * t]);
+          lowf = __int2float_rn((int)r[NL * t + 1] * 256 + (int)r[NL * t]);
         } else {
-          lowf = fmaf(__int2float_rn((int)r[3 * t + 1]), 256.f, __int2float_rn((int)r[3 * t]));
+          lowf = fmaf(__int2float_rn((int)r[NL * t + 1]), 256.f, __int2float_rn((int)r[NL * t]));
         }
-        total[c * 16 + t] = fmaf(sc, fmaf(__int2float_rn((int)r[3 * t + 2]), 65536.f, lowf), total[c * 16 + t]);
+        if constexpr (NL == 3) lowf = fmaf(__int2float_rn((int)r[NL * t + 2]), 65536.f, lowf);
+        total[c * 16 + t] = fmaf(sc, lowf, total[c * 16 + t]);
       }
     }
   }
 }
 
-template <int WBITS, int NCOLS>
-__global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, Cfg<WBITS, NCOLS>::kOcc)
+// The same for NREG accumulators in a row (`stride` columns apart, scale sc[i] each), with the tensor-memory loads of
+// the next 16 tokens in flight while the current ones are folded: a load's round trip otherwise sits between every
+// two chunks.  Costs a second set of 16 * NL registers.
+template <int NCOLS, int MT, int NL, bool SMALL, int NREG, typename Release>
+__device__ __forceinline__ void fold_regions_pipelined(uint32_t taddr, uint32_t stride, const float (&sc)[NREG], float (&total)[MT],
+                                                       Release release) {
+  constexpr int CW = 16 * NL;
+  constexpr int kChunks = (NCOLS + CW - 1) / CW;
+  constexpr int T = NREG * kChunks;
+  if constexpr (NREG == 1 && NCOLS <= 64) {
+    // one accumulator of up to 64 columns: all of it in one round trip
+    constexpr int L16 = (NCOLS + 15) / 16;
+    uint32_t v[16 * L16];
+#pragma unroll
+    for (int j = 0; j < L16; ++j) ptx::tmem_ld_32x32b_x16(taddr + 16 * j, v + 16 * j);
+    ptx::tmem_ld_wait();
+    release();
+    const float s0 = sc[0];
+#pragma unroll
+    for (int t = 0; t < MT; ++t) {
+      float lowf;
+      if (SMALL) {
+        lowf = __int2float_rn((int)v[NL * t + 1] * 256 + (int)v[NL * t]);
+      } else {
+        lowf = fmaf(__int2float_rn((int)v[NL * t + 1]), 256.f, __int2float_rn((int)v[NL * t]));
+      }
+      if constexpr (NL == 3) lowf = fmaf(__int2float_rn((int)v[NL * t + 2]), 65536.f, lowf);
+      total[t] = fmaf(s0, lowf, total[t]);
+    }
+    return;
+  }
+  uint32_t r[2][CW];
+  auto issue = [&](int i, uint32_t* dst) {
+    const int reg = i / kChunks, c = i % kChunks;
+#pragma unroll
+    for (int j = 0; j < NL; ++j)
+      if (c * CW + 16 * j < NCOLS) ptx::tmem_ld_32x32b_x16(taddr + reg * stride + c * CW + 16 * j, dst + 16 * j);
+  };
+
+  issue(0, r[0]);
+#pragma unroll
+  for (int i = 0; i < T; ++i) {
+    uint32_t* cur = r[i & 1];
+    ptx::tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < NL; ++j) ptx::tmem_ld_landed16(cur + 16 * j);
+    if (i + 1 < T) issue(i + 1, r[(i + 1) & 1]);
+    else release();  // the accumulators' last values are in registers
+    const int c = i % kChunks;
+    const float s = sc[i / kChunks];
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      if (c * 16 + t < MT) {
+        float lowf;
+        if (SMALL) {
+          lowf = __int2float_rn((int)cur[NL * t + 1] * 256 + (int)cur[NL * t]);
+        } else {
+          lowf = fmaf(__int2float_rn((int)cur[NL * t + 1]), 256.f, __int2float_rn((int)cur[NL * t]));
+        }
+        if constexpr (NL == 3) lowf = fmaf(__int2float_rn((int)cur[NL * t + 2]), 65536.f, lowf);
+        total[c * 16 + t] = fmaf(s, lowf, total[c * 16 + t]);
+      }
+    }
+  }
+}
+
+template <int WBITS, int NCOLS, int NL>
+__global__ void __launch_bounds__(Cfg<WBITS, NCOLS, NL>::kThreads, Cfg<WBITS, NCOLS, NL>::kOcc)
     limb_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const Params p) {
-  using C = Cfg<WBITS, NCOLS>;
+  using C = Cfg<WBITS, NCOLS, NL>;
   constexpr int kRaw = C::kRaw, kSlots = C::kSlots;
   constexpr uint32_t kBTile = C::kBTile, kSlot = C::kSlot;
   constexpr int MT = C::kTokens;
@@ -438,6 +559,7 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, Cfg<WBITS, NCOLS>
   if (warp == 0) {
     // ---------------- weight producer: needs nothing from earlier kernels, so it does not wait for them ----------------
     if (lane == 0) {
+      if (p.w_dep) asm volatile("griddepcontrol.wait;" ::: "memory");
       FragIter it(p);
       DBG_DECL;
       int tile, u0, u1, slot = 0;
@@ -483,8 +605,8 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, Cfg<WBITS, NCOLS>
           DBG_END(0);
           uint8_t* dst = slot_base + (size_t)slot * kSlot + C::kAInSlot;
           ptx::mbar_expect_tx(&full[slot], 2 * kBTile);
-          ptx::tma_load_2d(dst, &map_x, &full[slot], s * kSlotK, it.y * (3 * MT));
-          ptx::tma_load_2d(dst + kBTile, &map_x, &full[slot], s * kSlotK + kTileK, it.y * (3 * MT));
+          ptx::tma_load_2d(dst, &map_x, &full[slot], s * kSlotK, it.y * (NL * MT));
+          ptx::tma_load_2d(dst + kBTile, &map_x, &full[slot], s * kSlotK + kTileK, it.y * (NL * MT));
           if (++slot == kSlots) { slot = 0; ph ^= 1; }
         }
       }
@@ -599,13 +721,15 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, Cfg<WBITS, NCOLS>
     constexpr int MTD = MT / C::kHalves;                      // tokens per drain thread
     constexpr int DC = C::kHalves == 2 ? 64 : NCOLS;          // accumulator columns a thread loads per block
     const int half = (C::kHalves == 2 && warp >= C::kXDrainWarp0) ? 1 : 0;
-    const uint32_t col0 = (uint32_t)(half * 3 * MTD);
+    const uint32_t col0 = (uint32_t)(half * NL * MTD);
+    constexpr int kDT = 128 * C::kHalves;                     // drain threads
     const bool small = p.mode == kBlock128 || (p.mode == kBlockSlots && p.spu == 1);
     asm volatile("griddepcontrol.wait;" ::: "memory");  // pw, the scratch and `out` belong to earlier kernels until here
     if (warp == kDrainWarp0) { DBG_STAMP(5); }
     const int quad = warp & 3;
     const int rl = quad * 32 + lane;  // row inside the tile
-    const int dt = threadIdx.x - kDrainWarp0 * 32;  // 0..127 among the drain threads
+    const int dt = half ? 128 + (int)threadIdx.x - C::kXDrainWarp0 * 32 : (int)threadIdx.x - kDrainWarp0 * 32;  // 0..kDT-1
+    auto drain_bar = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(kDT) : "memory"); };
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
     const long long G = gridDim.x;
     FragIter it(p);
@@ -643,14 +767,27 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, Cfg<WBITS, NCOLS>
       int np = 0;
       bool fetched = false;
       auto add_partials = [&]() {
-        for (int j = 0; j < np; ++j) {
-          const float* src = p.partial + ((size_t)(blockIdx.x + 1 + j) * MT) * BMW + rl;
+        // two partial tiles in flight at a time (an L2 round trip each), added in CTA order
+        const float* src = p.partial + ((size_t)(blockIdx.x + 1) * MT + half * MTD) * BMW + rl;
+        constexpr size_t kTile = (size_t)MT * BMW;
+        int j = 0;
+        for (; C::kThreads <= 512 && j + 1 < np; j += 2) {  // (where the register budget allows)
+          float a[MTD], b[MTD];
+#pragma unroll
+          for (int t = 0; t < MTD; ++t) {
+            a[t] = t < mcount ? __ldcg(src + j * kTile + t * BMW) : 0.f;
+            b[t] = t < mcount ? __ldcg(src + (j + 1) * kTile + t * BMW) : 0.f;
+          }
+#pragma unroll
+          for (int t = 0; t < MTD; ++t) total[t] = (total[t] + a[t]) + b[t];
+        }
+        for (; j < np; ++j) {
 #pragma unroll
           for (int t = 0; t < MTD; ++t)
-            if (t < mcount) total[t] += __ldcg(src + t * BMW);
+            if (t < mcount) total[t] += __ldcg(src + j * kTile + t * BMW);
         }
         drain_bar();
-        for (int j = dt; j < np; j += 128) p.flags[blockIdx.x + 1 + j] = 0u;  // clean for the next launch
+        for (int j = dt; j < np; j += kDT) p.flags[blockIdx.x + 1 + j] = 0u;  // clean for the next launch
       };
       if (first && !last) {
         if (dt == 0) {
@@ -664,7 +801,7 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, Cfg<WBITS, NCOLS>
         }
         drain_bar();
         np = s_npart;
-        for (int j = dt; j < np; j += 128)
+        for (int j = dt; j < np; j += kDT)
           if (ld_acquire_gpu(p.flags + blockIdx.x + 1 + j) == 0u) s_ready = 0;
         drain_bar();
         fetched = s_ready != 0;
@@ -676,7 +813,7 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, Cfg<WBITS, NCOLS>
       float scq[kAhead];
       int b_next = p.mode == kBlock128 ? 2 * s0 : (p.mode == kBlockSlots ? s0 / p.spu : 0);
       auto fetch_scale = [&]() {
-        const float v = (p.mode != kPerChannel && n_ok && b_next < p.S) ? __ldg(p.scale + (int64_t)b_next * p.N + n) : 0.f;
+        const float v = (p.mode != kPerChannel && n_ok && b_next < p.S) ? __ldg(p.scale + (int64_t)b_next * p.ld + n) : 0.f;
         ++b_next;
         return v;
       };
@@ -695,8 +832,13 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, Cfg<WBITS, NCOLS>
             wait_acc();
             DBG_BEGIN();
             const uint32_t a = lane_addr + buf * (2 * NCOLS) + col0;
-            fold_region<DC, MTD, true>(a, pop_scale(), total, false, release);
-            fold_region<DC, MTD, true>(a + NCOLS, pop_scale(), total, true, release);
+            if constexpr (C::kPipeDrain) {
+              const float sc2[2] = {pop_scale(), pop_scale()};
+              fold_regions_pipelined<DC, MTD, NL, true, 2>(a, NCOLS, sc2, total, release);
+            } else {
+              fold_region<DC, MTD, NL, true>(a, pop_scale(), total, false, release);
+              fold_region<DC, MTD, NL, true>(a + NCOLS, pop_scale(), total, true, release);
+            }
             DBG_END(1);
             next_acc();
           } else {
@@ -704,7 +846,12 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, Cfg<WBITS, NCOLS>
             for (int h = 0; h < 2; ++h) {
               wait_acc();
               DBG_BEGIN();
-              fold_region<DC, MTD, true>(lane_addr + buf * NCOLS + col0, pop_scale(), total, true, release);
+              if constexpr (C::kPipeDrain) {
+                const float sc1[1] = {pop_scale()};
+                fold_regions_pipelined<DC, MTD, NL, true, 1>(lane_addr + buf * NCOLS + col0, 0, sc1, total, release);
+              } else {
+                fold_region<DC, MTD, NL, true>(lane_addr + buf * NCOLS + col0, pop_scale(), total, true, release);
+              }
               DBG_END(1);
               next_acc();
             }
@@ -717,8 +864,14 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, Cfg<WBITS, NCOLS>
           const float sc = p.mode == kPerChannel ? 1.f : pop_scale();
           wait_acc();
           DBG_BEGIN();
-          if (small) fold_region<DC, MTD, true>(lane_addr + buf * NCOLS + col0, sc, total, true, release);
-          else fold_region<DC, MTD, false>(lane_addr + buf * NCOLS + col0, sc, total, true, release);
+          if constexpr (C::kPipeDrain) {
+            const float sc1[1] = {sc};
+            if (small) fold_regions_pipelined<DC, MTD, NL, true, 1>(lane_addr + buf * NCOLS + col0, 0, sc1, total, release);
+            else fold_regions_pipelined<DC, MTD, NL, false, 1>(lane_addr + buf * NCOLS + col0, 0, sc1, total, release);
+          } else {
+            if (small) fold_region<DC, MTD, NL, true>(lane_addr + buf * NCOLS + col0, sc, total, true, release);
+            else fold_region<DC, MTD, NL, false>(lane_addr + buf * NCOLS + col0, sc, total, true, release);
+          }
           DBG_END(1);
           next_acc();
           s = g_end;
@@ -728,7 +881,7 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, Cfg<WBITS, NCOLS>
       // ---- end of the fragment ----
       if (!first) {
         // a later K range of a tile that another CTA started: leave the partial sums for that CTA
-        float* dst = p.partial + ((size_t)blockIdx.x * MT) * BMW + rl;
+        float* dst = p.partial + ((size_t)blockIdx.x * MT + half * MTD) * BMW + rl;
 #pragma unroll
         for (int t = 0; t < MTD; ++t)
           if (t < mcount) __stcg(dst + t * BMW, total[t]);
@@ -740,7 +893,7 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, Cfg<WBITS, NCOLS>
       }
       if (!last && !fetched) {
         // add the partial sums of the CTAs that continue the tile, in CTA order
-        for (int j = dt; j < np; j += 128) {
+        for (int j = dt; j < np; j += kDT) {
           const uint32_t* f = p.flags + blockIdx.x + 1 + j;
           const long long t0 = clock64();
           uint32_t spins = 0;
@@ -760,7 +913,7 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, Cfg<WBITS, NCOLS>
 #pragma unroll
         for (int t = 0; t < MTD; ++t)
           if (t < mcount && n_ok)
-            store_from_f32(p.out, (int64_t)(p.m0 + mt0 + t) * p.N + n, p.out_dt, total[t] * ps * __ldg(p.pw + mt0 + t));
+            store_from_f32(p.out, (int64_t)(p.m0 + mt0 + t) * p.ld + n, p.out_dt, total[t] * ps * __ldg(p.pw + mt0 + t));
       } else {
         // rows come in groups of 16: eight gate rows, then the eight up rows of the same outputs
 #pragma unroll
@@ -768,7 +921,7 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS>::kThreads, Cfg<WBITS, NCOLS>
           const float v = t < mcount ? total[t] * ps * __ldg(p.pw + mt0 + t) : 0.f;
           const float u = __shfl_down_sync(0xffffffffu, v, 8);
           if (t < mcount && n_ok && (rl & 8) == 0)
-            store_from_f32(p.out, (int64_t)(p.m0 + mt0 + t) * (p.N >> 1) + gate_up_column(n), p.out_dt, silu_mul(v, u));
+            store_from_f32(p.out, (int64_t)(p.m0 + mt0 + t) * (p.ld >> 1) + gate_up_column(n), p.out_dt, silu_mul(v, u));
         }
       }
       DBG_END(2);
@@ -866,20 +1019,44 @@ struct Scratch {
   size_t bytes;
 };
 
-int ncols_for(int64_t M) {
-  if (M <= 5) return 16;
-  if (M <= 10) return 32;
-  if (M <= 16) return 48;
-  if (M <= 32) return 96;
-  return 128;  // larger batches: token tiles of 42 (126 limb columns), see launch_limb_tc
-}
+// How one launch is laid out: limbs per token, limb columns per tile (the template instance), and whether the K axis
+// is split over the CTAs (stream-K, one token tile) or the batch runs as (weight tile, token tile) items.
+struct Plan {
+  int nl, ncols, tile_tokens;
+  bool items;
+};
 
-constexpr int kItemTokens = 42;                    // Cfg<*, 128>::kTokens
-constexpr int64_t kLimbMaxRows = 24 * kItemTokens;  // tokens per launch in item mode (1008); longer batches are chunked
+// limb_tc_set_limbs(3) keeps three limbs everywhere (process-wide).
+std::atomic<int> g_limb_policy{0};
+
+// Limbs per token.  In narrow tiles the MMA costs the same with three limbs as with two, so the exact form is kept
+// there.  Wider batches pay per limb column: when the output is a 16-bit type, two limbs (15 bits below the row's
+// largest value, error at most 2^-15 of it per activation, under the output's own rounding) carry 64 tokens per
+// 128-column tile instead of 42.  fp32 outputs always get three.
+Plan plan_for(int wbits, int64_t M, int out_dt) {
+  const bool two_ok = g_limb_policy.load(std::memory_order_relaxed) != 3 && (out_dt == QMM_BF16 || out_dt == QMM_F16);
+  Plan pl;
+  pl.nl = 3;
+  pl.items = false;
+  if (M <= 5) pl.ncols = 16;
+  else if (M <= 10) pl.ncols = 32;
+  else if (M <= 16) pl.ncols = 48;
+  else if (M <= 32 && !(wbits == 4 && two_ok)) pl.ncols = 96;
+  else {
+    // 128 columns: 42 tokens of three limbs or 64 of two; one tile is split over K, more run as items
+    pl.ncols = 128;
+    pl.nl = two_ok ? 2 : 3;
+    pl.items = M > (pl.nl == 2 ? 64 : 42);
+  }
+  pl.tile_tokens = pl.ncols / pl.nl;
+  return pl;
+}
+// tokens per launch above which a batch is chunked (24 tiles of 42, 16 tiles of 64)
+int64_t max_rows(int nl) { return nl == 2 ? 1024 : 1008; }
 
 // Layout of the caller's scratch: [flags: 1 KB][pw][limbs][partial tiles]; the flag words come first so that a
-// caller who clears only the head of the buffer clears them.
-Scratch carve(void* base, int64_t M, int64_t K, int max_ctas) {
+// caller who clears only the head of the buffer clears them.  partial_tokens: tokens of a stream-K tile, 0 for items.
+Scratch carve(void* base, int64_t M, int64_t K, int nl, int partial_tokens, int max_ctas) {
   Scratch s;
   uint8_t* b = reinterpret_cast<uint8_t*>(base);
   size_t off = 0;
@@ -888,17 +1065,17 @@ Scratch carve(void* base, int64_t M, int64_t K, int max_ctas) {
   s.pw = reinterpret_cast<float*>(b + off);
   off += align_up((size_t)M * 4, 256);
   s.limbs = reinterpret_cast<int8_t*>(b + off);
-  off += align_up((size_t)3 * M * K, 256);
+  off += align_up((size_t)nl * M * K, 256);
   s.partial = reinterpret_cast<float*>(b + off);
-  if (ncols_for(M) != 128) off += (size_t)max_ctas * (ncols_for(M) / 3) * BMW * 4;  // item mode exchanges nothing
+  off += align_up((size_t)max_ctas * partial_tokens * BMW * 4, 256);
   s.bytes = off;
   return s;
 }
 
-template <int WBITS, int NCOLS>
+template <int WBITS, int NCOLS, int NL = 3>
 int launch_cfg(const CUtensorMap& map_w, const CUtensorMap& map_x, const Params& p, int grid, cudaStream_t st) {
-  using C = Cfg<WBITS, NCOLS>;
-  auto kern = limb_tc_kernel<WBITS, NCOLS>;
+  using C = Cfg<WBITS, NCOLS, NL>;
+  auto kern = limb_tc_kernel<WBITS, NCOLS, NL>;
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -926,7 +1103,15 @@ int launch_cfg(const CUtensorMap& map_w, const CUtensorMap& map_x, const Params&
 }
 
 template <int WBITS>
-int launch_ncols(int ncols, const CUtensorMap& map_w, const CUtensorMap& map_x, const Params& p, int grid, cudaStream_t st) {
+int launch_ncols(int ncols, int nl, const CUtensorMap& map_w, const CUtensorMap& map_x, const Params& p, int grid, cudaStream_t st) {
+  if (nl == 2) {
+    switch (ncols) {
+      case 16: return launch_cfg<WBITS, 16, 2>(map_w, map_x, p, grid, st);
+      case 32: return launch_cfg<WBITS, 32, 2>(map_w, map_x, p, grid, st);
+      case 64: return launch_cfg<WBITS, 64, 2>(map_w, map_x, p, grid, st);
+      default: return launch_cfg<WBITS, 128, 2>(map_w, map_x, p, grid, st);
+    }
+  }
   switch (ncols) {
     case 16: return launch_cfg<WBITS, 16>(map_w, map_x, p, grid, st);
     case 32: return launch_cfg<WBITS, 32>(map_w, map_x, p, grid, st);
@@ -937,7 +1122,7 @@ int launch_ncols(int ncols, const CUtensorMap& map_w, const CUtensorMap& map_x, 
 }
 
 template <typename XT>
-cudaError_t launch_split(const void* x, int8_t* xl, float* pw, int64_t M, int64_t K, int perm4, float pw_mul, cudaStream_t st) {
+cudaError_t launch_split(const void* x, int8_t* xl, float* pw, int64_t M, int64_t K, int nl, int perm4, float pw_mul, cudaStream_t st) {
   int threads = (int)std::min<int64_t>(1024, std::max<int64_t>(64, align_up((size_t)(K / 8), 32)));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)M);
@@ -948,14 +1133,111 @@ cudaError_t launch_split(const void* x, int8_t* xl, float* pw, int64_t M, int64_
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, split_rows_kernel<XT>, reinterpret_cast<const XT*>(x), xl, pw, K, perm4, pw_mul);
+  if (nl == 2) return cudaLaunchKernelEx(&cfg, split_rows_kernel<XT, 2>, reinterpret_cast<const XT*>(x), xl, pw, K, perm4, pw_mul);
+  return cudaLaunchKernelEx(&cfg, split_rows_kernel<XT, 3>, reinterpret_cast<const XT*>(x), xl, pw, K, perm4, pw_mul);
 }
 
 }  // namespace
 
+namespace {
+
+// int4 batches at least this long are expanded to int8 once when the caller gave room: the pass over the weights is
+// paid back sooner per channel (the int8 form then runs with no hand-over inside a tile) than with scale blocks
+constexpr int64_t kExpandTokens = 384, kExpandTokensBlockwise = 768;
+
+// Work split of one token tile.  Stream-K (equal shares of the tile x K-slot units) keeps every SM streaming, but a
+// tile shared by several CTAs costs a partial-tile exchange through L2 at the end of the kernel, worth a few slots of
+// streaming.  When handing out whole tiles costs fewer slots per CTA than that, each CTA gets whole tiles and
+// nothing is exchanged.  Every CTA should stream at least two slots, or its fixed cost dominates.
+struct Split {
+  int grid;
+  long long cost;  // slots of streaming per SM, exchange included
+};
+Split split_one_tile(int wbits, const Plan& pl, long long tiles, long long slots, int spu) {
+  const long long ut = ceil_div(slots, spu), units = tiles * ut;
+  const int occ = (wbits == 4 && pl.ncols <= 48) ? 2 : 1;  // Cfg::kOcc
+  const long long ctas_max = std::min<long long>((long long)occ * sm_count(), kLimbMaxCtas);
+  const long long min_units = std::max<long long>(1, 2 / spu);
+  Split sp;
+  sp.grid = (int)std::min<long long>(ctas_max, std::max<long long>(1, units / min_units));
+  const long long sk_slots = ceil_div(units, sp.grid) * spu;                  // slots per CTA, stream-K
+  const long long per_sm = occ;                                               // CTAs that share an SM's bandwidth
+  const long long dp_rounds = ceil_div(tiles, ctas_max);
+  const long long dp_slots = dp_rounds * slots;                               // slots per CTA, whole tiles
+  // exchange cost in slots of streaming (measured: ~3 us for tiles of 5 tokens, ~13 us for 64); a partial tile is
+  // 128 x tokens floats, so it grows with the tile
+  const long long exchange = (wbits == 4 ? 8 : 4) * (16 + pl.tile_tokens) / 16;
+  // compare per-SM streaming: with whole tiles only ceil(tiles / rounds) CTAs run, spread over the SMs
+  const long long dp_ctas = ceil_div(tiles, dp_rounds);
+  const long long dp_per_sm = ceil_div(dp_ctas, sm_count());
+  const bool fills = occ == 1 || dp_ctas * 4 >= ctas_max * 3;  // two CTAs per SM only pay off when both slots are used
+  sp.cost = sk_slots * per_sm + exchange;
+  if (fills && dp_slots * dp_per_sm <= sp.cost && tiles <= ctas_max * dp_rounds) {
+    sp.cost = dp_slots * dp_per_sm;
+    sp.grid = (int)std::min<long long>(tiles, ctas_max);
+    // with several rounds the units must still split at tile boundaries: a grid that divides the tile count
+    while (tiles % sp.grid != 0) --sp.grid;
+  }
+  return sp;
+}
+
+// Few weight tiles (a narrow layer, a tensor-parallel shard): with the widest token tile only `tiles` CTAs would get a
+// whole-K item, and splitting K instead costs the exchange, which grows with the tile.  Narrower token tiles give
+// more CTAs a whole-K item each (an MMA costs the same for any width up to 128 columns, and the tensor pipe is idle
+// here anyway); the weight tile is then read by several CTAs, from L2.
+void narrow_for_few_tiles(Plan& pl, int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size) {
+  const long long tiles = ceil_div(N, BMW), sms = sm_count(), slots = ceil_div(K, kSlotK);
+  const long long y0 = pl.items ? ceil_div(M, pl.tile_tokens) : 1;
+  if (tiles * y0 * 4 >= sms * 3) return;  // most SMs have an item already
+  static const int w3[] = {128, 96, 48, 32, 16}, w2[] = {128, 64, 32, 16};
+  const int* ws = pl.nl == 2 ? w2 : w3;
+  const int nw = pl.nl == 2 ? 4 : 5;
+  int pick = 0;
+  for (int i = 0; i < nw; ++i) {
+    if (ws[i] > pl.ncols) continue;
+    pick = ws[i];
+    if (tiles * ceil_div(M, ws[i] / pl.nl) * 4 >= sms * 3) break;
+  }
+  const long long y = ceil_div(M, pick / pl.nl);
+  if (pick == 0 || y <= y0) return;  // no narrower tile gives more items
+  const long long cand = ceil_div(tiles * y, sms) * slots;
+  const int spu = (block_size > 0 && block_size != kTileK) ? (int)(block_size / kSlotK) : 1;
+  const long long base = pl.items ? ceil_div(tiles * y0, sms) * slots : split_one_tile(wbits, pl, tiles, slots, spu).cost;
+  if (cand >= base) return;
+  pl.ncols = pick;
+  pl.tile_tokens = pick / pl.nl;
+  pl.items = true;
+}
+
+// One launch of the main kernel over `rows` weight rows at `w` (row pitch K * wbits / 8 bytes).
+int launch_main(int wbits, const void* w, int64_t rows, int64_t K, const Plan& pl, Params p, const CUtensorMap& map_x, cudaStream_t st) {
+  const int ncols = pl.ncols;
+  p.N = rows;
+  p.tiles = (int)ceil_div(rows, BMW);
+  p.units = (long long)p.tiles * p.ut;
+  int grid;
+  if (pl.items) {
+    // the CTAs walk the (weight tile, token tile) items; nothing is exchanged between them
+    const int occ = (wbits == 4 && ncols <= 48) ? 2 : 1;  // Cfg::kOcc
+    grid = (int)std::min<long long>((long long)occ * sm_count(), (long long)p.tiles * p.ytiles);
+  } else {
+    grid = split_one_tile(wbits, pl, p.tiles, p.slots, p.spu).grid;
+  }
+  CUtensorMap map_w;
+  const int rc = encode_tmap_2d(&map_w, w, 1, false, (uint64_t)rows, (uint64_t)(K * wbits / 8), BMW, 128);
+  if (rc != QMM_OK) return rc;
+  return wbits == 4 ? launch_ncols<4>(ncols, pl.nl, map_w, map_x, p, grid, st) : launch_ncols<8>(ncols, pl.nl, map_w, map_x, p, grid, st);
+}
+
+}  // namespace
+
+void limb_tc_set_limbs(int limbs) { g_limb_policy.store(limbs == 3 ? 3 : 0, std::memory_order_relaxed); }
+
 size_t limb_tc_workspace_bytes(int64_t M, int64_t K) {
   if (M < 1 || K < 1) return 0;
-  return carve(nullptr, std::min(M, kLimbMaxRows), K, kLimbMaxCtas).bytes;
+  // Enough for either limb form (the output type is not known here) and for every batch up to M: the limbs of the
+  // longest chunk, and the partial tiles of the widest stream-K batch that is not longer than M.
+  return carve(nullptr, std::min(M, max_rows(3)), K, 3, (int)std::min<int64_t>(M, 64), kLimbMaxCtas).bytes;
 }
 
 bool limb_tc_shape_ok(int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size, int x_dt, bool has_zp) {
@@ -991,9 +1273,27 @@ bool limb_tc_preferred(int wbits, int64_t M, int64_t N, int64_t K, int64_t block
   return mib >= 48;
 }
 
-int launch_limb_tc(int wbits, const void* x, int x_dt, const void* w, const float* scale, void* out, int out_dt, int64_t M,
-                   int64_t N, int64_t K, int64_t block_size, int gate_up, void* workspace, size_t workspace_bytes,
-                   cudaStream_t st) {
+namespace {
+
+cudaError_t launch_expand(const void* src, void* dst, int64_t rows, int64_t K, cudaStream_t st) {
+  const int64_t chunks = rows * K / 16;  // 8 packed bytes each
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)std::min<int64_t>(ceil_div(chunks, 256 * 4), 8LL * sm_count()));
+  cfg.blockDim = dim3(256);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, expand_int4_kernel, reinterpret_cast<const uint2*>(src), reinterpret_cast<uint4*>(dst), chunks);
+}
+
+// pw_mul: factor folded into the per-token power of two (1/16 when the weight bytes hold value * 16); w_dep: the
+// weights are written by a kernel earlier in the stream that the weight producer has to wait for.
+int launch_limb_impl(int wbits, const void* x, int x_dt, const void* w, const float* scale, void* out, int out_dt, int64_t M,
+                     int64_t N, int64_t K, int64_t block_size, int gate_up, void* workspace, size_t workspace_bytes,
+                     float pw_mul, int w_dep, cudaStream_t st) {
   if (!limb_tc_supported(wbits, M, N, K, block_size, x, x_dt, w, false))
     return fail(QMM_ERR_UNSUPPORTED,
                 "split-activation tensor-core kernel: needs an sm_100 device, K >= 128 and a multiple of %d, "
@@ -1001,98 +1301,125 @@ int launch_limb_tc(int wbits, const void* x, int x_dt, const void* w, const floa
                 wbits == 8 ? 16 : 32, (long long)M, (long long)N, (long long)K, (long long)block_size);
   if (gate_up && N % 16 != 0)
     return fail(QMM_ERR_BAD_SHAPE, "fused gate/up epilogue: the interleaved weight needs a multiple of 16 rows, got %lld", (long long)N);
-  const size_t need = limb_tc_workspace_bytes(M, K);
+  Plan pl = plan_for(wbits, M, out_dt);
+  if (M <= max_rows(pl.nl)) narrow_for_few_tiles(pl, wbits, M, N, K, block_size);
+  const int nl = pl.nl;
+  const size_t need = carve(nullptr, std::min(M, max_rows(nl)), K, nl, pl.items ? 0 : pl.tile_tokens, kLimbMaxCtas).bytes;
   if (!workspace || workspace_bytes < need)
     return fail(QMM_ERR_WORKSPACE, "split-activation tensor-core kernel needs %zu bytes of workspace, got %zu", need, workspace_bytes);
   if (!aligned(workspace, 256)) return fail(QMM_ERR_MISALIGNED, "workspace must be 256-byte aligned");
-  if (M > kLimbMaxRows) {
+  // int4 and a long batch: with room in the workspace behind the regular scratch, the weights are expanded to int8
+  // once and the int8 form of the kernel runs on them (all of them if they fit, else slice by slice, see below)
+  const bool widen = wbits == 4 && M >= (block_size > 0 ? kExpandTokensBlockwise : kExpandTokens) && !gate_up;
+  const size_t wide_off = align_up(need, 256);
+  if (widen && workspace_bytes >= wide_off + (size_t)N * (size_t)K) {
+    uint8_t* wide = reinterpret_cast<uint8_t*>(workspace) + wide_off;
+    cudaError_t e = launch_expand(w, wide, N, K, st);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(QMM_ERR_LAUNCH, "expand_int4_kernel launch: %s", cudaGetErrorString(e));
+    }
+    return launch_limb_impl(8, x, x_dt, wide, scale, out, out_dt, M, N, K, block_size, 0, workspace, wide_off, 0.0625f, 1, st);
+  }
+  if (M > max_rows(nl)) {
     // long batches run in chunks of whole token tiles that share the scratch (same stream: ordered)
-    if (gate_up) return fail(QMM_ERR_UNSUPPORTED, "fused gate/up epilogue: at most %lld tokens per call", (long long)kLimbMaxRows);
+    const int64_t rows = max_rows(nl);
+    if (gate_up) return fail(QMM_ERR_UNSUPPORTED, "fused gate/up epilogue: at most %lld tokens per call", (long long)rows);
     const size_t xb = dtype_size(x_dt), ob = dtype_size(out_dt);
-    for (int64_t m0 = 0; m0 < M; m0 += kLimbMaxRows) {
-      const int64_t mc = std::min(kLimbMaxRows, M - m0);
-      const int rc = launch_limb_tc(wbits, reinterpret_cast<const uint8_t*>(x) + (size_t)m0 * K * xb, x_dt, w, scale,
-                                    reinterpret_cast<uint8_t*>(out) + (size_t)m0 * N * ob, out_dt, mc, N, K, block_size, 0, workspace,
-                                    workspace_bytes, st);
+    for (int64_t m0 = 0; m0 < M; m0 += rows) {
+      const int64_t mc = std::min(rows, M - m0);
+      const int rc = launch_limb_impl(wbits, reinterpret_cast<const uint8_t*>(x) + (size_t)m0 * K * xb, x_dt, w, scale,
+                                      reinterpret_cast<uint8_t*>(out) + (size_t)m0 * N * ob, out_dt, mc, N, K, block_size, 0, workspace,
+                                      workspace_bytes, pw_mul, w_dep, st);
       if (rc != QMM_OK) return rc;
     }
     return QMM_OK;
   }
-  const Scratch sc = carve(workspace, M, K, kLimbMaxCtas);
-  const int ncols = ncols_for(M);
-  const bool items = ncols == 128;
+  const Scratch sc = carve(workspace, M, K, nl, pl.items ? 0 : pl.tile_tokens, kLimbMaxCtas);
 
-  Params p;
-  p.scale = scale;
-  p.pw = sc.pw;
-  p.out = out;
-  p.out_dt = out_dt;
-  p.M = (int)M;
-  p.N = N;
-  p.tiles = (int)ceil_div(N, BMW);
-  p.slots = (int)ceil_div(K, kSlotK);
-  p.mode = block_size <= 0 ? kPerChannel : (block_size == kTileK ? kBlock128 : kBlockSlots);
-  p.S = block_size > 0 ? (int)(K / block_size) : 1;
-  p.spu = p.mode == kBlockSlots ? (int)(block_size / kSlotK) : 1;
-  p.ut = (int)ceil_div(p.slots, p.spu);
-  p.units = (long long)p.tiles * p.ut;
-  p.partial = sc.partial;
-  p.flags = sc.flags;
-  p.err_word = device_error_word();
-  p.gate_up = gate_up;
-  p.ytiles = items ? (int)ceil_div(M, kItemTokens) : 0;
-  p.m0 = 0;
-  int grid;
-  if (items) {
-    // one CTA per SM walks the (weight tile, token tile) items; nothing is exchanged between CTAs
-    grid = (int)std::min<long long>(sm_count(), (long long)p.tiles * p.ytiles);
-  } else {
-    // Work split.  Stream-K (equal shares of the tile x K-slot units) keeps every SM streaming, but a tile shared by
-    // several CTAs costs a partial-tile exchange through L2 at the end of the kernel, worth a few slots of
-    // streaming.  When handing out whole tiles costs fewer slots per CTA than that, each CTA gets whole tiles and
-    // nothing is exchanged.  Every CTA should stream at least two slots, or its fixed cost dominates.
-    const int occ = (wbits == 4 && ncols <= 48) ? 2 : 1;  // Cfg::kOcc
-    const long long ctas_max = std::min<long long>((long long)occ * sm_count(), kLimbMaxCtas);
-    const long long min_units = std::max<long long>(1, 2 / p.spu);
-    grid = (int)std::min<long long>(ctas_max, std::max<long long>(1, p.units / min_units));
-    const long long sk_slots = ceil_div(p.units, grid) * p.spu;                 // slots per CTA, stream-K
-    const long long per_sm = occ;                                               // CTAs that share an SM's bandwidth
-    const long long dp_rounds = ceil_div(p.tiles, ctas_max);
-    const long long dp_slots = dp_rounds * p.slots;                             // slots per CTA, whole tiles
-    // exchange cost in slots of streaming (measured); a partial tile is 128 x M floats, so it grows with the batch
-    const long long exchange = (wbits == 4 ? 8 : 4) * std::max(1, ncols / 48);
-    // compare per-SM streaming: with whole tiles only ceil(tiles / rounds) CTAs run, spread over the SMs
-    const long long dp_ctas = ceil_div(p.tiles, dp_rounds);
-    const long long dp_per_sm = ceil_div(dp_ctas, sm_count());
-    const bool fills = occ == 1 || dp_ctas * 4 >= ctas_max * 3;  // two CTAs per SM only pay off when both slots are used
-    if (fills && dp_slots * dp_per_sm <= sk_slots * per_sm + exchange && p.tiles <= ctas_max * dp_rounds) {
-      grid = (int)std::min<long long>(p.tiles, ctas_max);
-      // with several rounds the units must still split at tile boundaries: a grid that divides the tile count
-      while (p.tiles % grid != 0) --grid;
+  // slices of weight rows that fit behind the scratch, expanded and multiplied one after the other
+  int64_t slice_rows = 0;
+  uint8_t* wide = nullptr;
+  if (widen && workspace_bytes > wide_off) {
+    wide = reinterpret_cast<uint8_t*>(workspace) + wide_off;
+    const size_t room = workspace_bytes - wide_off;
+    const int64_t fit = (int64_t)(room / (size_t)K) / BMW * BMW;  // whole weight tiles
+    // a slice must still give every SM a few items, or the GEMM's last wave eats the gain
+    const int64_t ytiles = ceil_div(M, pl.tile_tokens);
+    const int64_t min_rows = std::min<int64_t>(align_up((size_t)N, BMW), ceil_div(3 * (int64_t)sm_count(), ytiles) * BMW);
+    if (fit >= min_rows) {
+      const int64_t n_slices = ceil_div(N, fit);
+      slice_rows = align_up((size_t)ceil_div(N, n_slices), BMW);
     }
   }
 
-  CUtensorMap map_w, map_x;
-  int rc = encode_tmap_2d(&map_w, w, 1, false, (uint64_t)N, (uint64_t)(K * wbits / 8), BMW, 128);
-  if (rc != QMM_OK) return rc;
-  rc = encode_tmap_2d(&map_x, sc.limbs, 1, false, (uint64_t)(3 * M), (uint64_t)K, (uint32_t)ncols, 128);
-  if (rc != QMM_OK) return rc;
-
-  const float pw_mul = wbits == 4 ? 0.0625f : 1.f;
   {
     // the limbs are made by a kernel of their own (one CTA per token) and reach the main kernel as TMA tiles; the two
     // are chained with programmatic dependent launch, so the main kernel's set-up and first weight loads run under it
+    const int perm4 = wbits == 4 && slice_rows == 0;  // the expanded weights are in natural k order
     cudaError_t e;
-    if (x_dt == QMM_F32) e = launch_split<float>(x, sc.limbs, sc.pw, M, K, wbits == 4, pw_mul, st);
-    else if (x_dt == QMM_BF16) e = launch_split<__nv_bfloat16>(x, sc.limbs, sc.pw, M, K, wbits == 4, pw_mul, st);
-    else e = launch_split<__half>(x, sc.limbs, sc.pw, M, K, wbits == 4, pw_mul, st);
+    if (x_dt == QMM_F32) e = launch_split<float>(x, sc.limbs, sc.pw, M, K, nl, perm4, pw_mul, st);
+    else if (x_dt == QMM_BF16) e = launch_split<__nv_bfloat16>(x, sc.limbs, sc.pw, M, K, nl, perm4, pw_mul, st);
+    else e = launch_split<__half>(x, sc.limbs, sc.pw, M, K, nl, perm4, pw_mul, st);
     if (e != cudaSuccess) {
       cudaGetLastError();
       return fail(QMM_ERR_LAUNCH, "split_rows_kernel launch: %s", cudaGetErrorString(e));
     }
   }
-  int rcl = wbits == 4 ? launch_ncols<4>(ncols, map_w, map_x, p, grid, st) : launch_ncols<8>(ncols, map_w, map_x, p, grid, st);
-  return rcl;
+  CUtensorMap map_x;
+  int rc = encode_tmap_2d(&map_x, sc.limbs, 1, false, (uint64_t)(nl * M), (uint64_t)K, (uint32_t)pl.ncols, 128);
+  if (rc != QMM_OK) return rc;
+
+  Params p;
+  p.pw = sc.pw;
+  p.out_dt = out_dt;
+  p.M = (int)M;
+  p.ld = N;
+  p.slots = (int)ceil_div(K, kSlotK);
+  p.mode = block_size <= 0 ? kPerChannel : (block_size == kTileK ? kBlock128 : kBlockSlots);
+  p.S = block_size > 0 ? (int)(K / block_size) : 1;
+  p.spu = p.mode == kBlockSlots ? (int)(block_size / kSlotK) : 1;
+  p.ut = (int)ceil_div(p.slots, p.spu);
+  p.partial = sc.partial;
+  p.flags = sc.flags;
+  p.err_word = device_error_word();
+  p.gate_up = gate_up;
+  p.ytiles = pl.items ? (int)ceil_div(M, pl.tile_tokens) : 0;
+  p.m0 = 0;
+  if (slice_rows == 0) {
+    p.scale = scale;
+    p.out = out;
+    p.w_dep = w_dep;
+    return launch_main(wbits, w, N, K, pl, p, map_x, st);
+  }
+  const size_t ob = dtype_size(out_dt);
+  for (int64_t n0 = 0; n0 < N; n0 += slice_rows) {
+    const int64_t rows = std::min(slice_rows, N - n0);
+    cudaError_t e = launch_expand(reinterpret_cast<const uint8_t*>(w) + (size_t)n0 * (size_t)(K / 2), wide, rows, K, st);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(QMM_ERR_LAUNCH, "expand_int4_kernel launch: %s", cudaGetErrorString(e));
+    }
+    p.scale = scale + n0;
+    p.out = reinterpret_cast<uint8_t*>(out) + (size_t)n0 * ob;
+    p.w_dep = 1;
+    rc = launch_main(8, wide, rows, K, pl, p, map_x, st);
+    if (rc != QMM_OK) return rc;
+  }
+  return QMM_OK;
+}
+
+}  // namespace
+
+int launch_limb_tc(int wbits, const void* x, int x_dt, const void* w, const float* scale, void* out, int out_dt, int64_t M,
+                   int64_t N, int64_t K, int64_t block_size, int gate_up, void* workspace, size_t workspace_bytes,
+                   cudaStream_t st) {
+  return launch_limb_impl(wbits, x, x_dt, w, scale, out, out_dt, M, N, K, block_size, gate_up, workspace, workspace_bytes,
+                          wbits == 4 ? 0.0625f : 1.f, 0, st);
+}
+
+size_t limb_tc_wide_bytes(int wbits, int64_t M, int64_t N, int64_t K) {
+  return (wbits == 4 && M >= kExpandTokens) ? 256 + (size_t)N * (size_t)K : 0;
 }
 
 }  // namespace qmm

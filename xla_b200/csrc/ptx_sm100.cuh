@@ -293,6 +293,15 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t* r) 
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// After a tmem_ld_wait that follows OTHER instructions issued since the load: tells the compiler that the 16
+// registers of that load change here, so that it neither reads nor moves them between the load and the wait.
+__device__ __forceinline__ void tmem_ld_landed16(uint32_t* r) {
+  asm volatile(""
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                 "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+               :
+               : "memory");
+}
 
 // ---- registers -> TMEM --------------------------------------------------------------------
 // Each thread of the warp writes 16 consecutive 32-bit columns of its own TMEM lane.

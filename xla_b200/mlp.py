@@ -85,6 +85,26 @@ def quantized_gate_up(x, w, scaler, block_size=-1, int4_weight=False, weight_is_
 
     out = _capi.on_device(x.device, run)
   else:
+    out = None
+    if (32 < M <= 1008 and x2.dtype in (torch.bfloat16, torch.float16, torch.float32) and K >= 128 and K % (128 // wbits) == 0 and
+        (block_size == -1 or block_size == 128 or block_size % 256 == 0) and _qm.current_variant() in ("auto", "i8tc")):
+      # larger batches: the split-activation tensor-core kernel applies silu(gate) * up in its drain
+      expect = (N2,) if block_size == -1 else (K // block_size, N2)
+      assert tuple(s32.shape) == expect, f"weight scaler shape is expect to be {list(expect)}, got {list(s32.shape)}."
+      wc = w if w.is_contiguous() else w.contiguous()
+
+      def run():
+        ws, ws_bytes = _capi.workspace(x.device, M, K)
+        if ws is None:  # a stream capture that began before the scratch existed
+          return None
+        res = torch.empty((M, N2 // 2), dtype=out_dtype, device=x.device)
+        _capi.check(_capi.lib().qmm_gate_up(wbits, x2.data_ptr(), _capi.dtype_code(x2.dtype), wc.data_ptr(), s32.data_ptr(),
+                                            res.data_ptr(), _capi.dtype_code(out_dtype), M, N2, K,
+                                            0 if block_size == -1 else block_size, ws, ws_bytes, _capi.stream_ptr(x.device)))
+        return res
+
+      out = _capi.on_device(x.device, run)
+  if out is None:
     y = quantized_matmul_packed(x2, w, s32, None, block_size=block_size, int4_weight=int4_weight,
                                 weight_is_packed=weight_is_packed, out_dtype=torch.float32)
     g, u = _deinterleave(y)

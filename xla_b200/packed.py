@@ -123,7 +123,7 @@ def quantized_matmul_packed(x, w, scaler, zero_point=None, block_size=-1, int4_w
     else:
       out = torch.empty((M, N), dtype=kdt, device=x.device)
     st = _capi.stream_ptr(x.device)
-    ws, ws_bytes = _capi.workspace(x.device, M, K)
+    ws, ws_bytes = _capi.workspace(x.device, M, K, N, 4 if weight_is_packed else 8)
     _capi.check(L.qmm_weight_only(4 if weight_is_packed else 8, x2.data_ptr(), _capi.dtype_code(x2.dtype), w.data_ptr(),
                                   s32.data_ptr(), None if zp_after else _capi.ptr(zp32), out.data_ptr(), _capi.dtype_code(kdt),
                                   M, N, K, 0 if block_size == -1 else block_size, variant, ws, ws_bytes, st))

@@ -203,6 +203,13 @@ _kminor_cache = {}
 _kminor_enabled = True
 
 
+def set_activation_limbs(limbs: int):
+  """Precision of the split-activation kernel above 32 tokens (process-wide).  0, the default: bf16 / f16 outputs take
+  two int8 limbs per activation (error at most 2^-15 of the row's largest |x| each), fp32 outputs three; 3: three
+  limbs everywhere, the accuracy of an fp32 accumulation, at a third more tensor-core columns per token."""
+  _capi.check(_capi.lib().qmm_set_activation_limbs(int(limbs)))
+
+
 def set_prepack_cache(enabled: bool):
   """Turns the operator's K-minor weight cache on or off (off: every blockwise call on the reference layout runs
   the any-shape kernel) and drops what it holds."""
