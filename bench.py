@@ -578,10 +578,31 @@ def run_ours(args, rank, world, local_rank):
     hy = {m: torch.empty(m, H, dtype=torch.bfloat16).pin_memory() for m in MS}
     e2e_reps = max(1, min(reps, 4))
 
+    # With several GPUs the host link is the scarce resource: every rank needs the whole batch, but only a 1/N
+    # slice of it has to cross that rank's PCIe link - the ranks gather the slices over NVLink - and the result, which
+    # is identical on all ranks after the exchange, is read by rank 0 alone.  (Bytes per step below are rank 0's.)
+    def sliced(m):
+      return world > 1 and m % world == 0
+
+    def copy_in(m, dst=None):
+      if not sliced(m):
+        if dst is None:
+          return hx[m].to(dev, non_blocking=True)
+        dst.copy_(hx[m], non_blocking=True)
+        return dst
+      rows = m // world
+      part = hx[m][rank * rows:(rank + 1) * rows].to(dev, non_blocking=True)
+      full = torch.empty(m, H, dtype=torch.bfloat16, device=dev) if dst is None else dst
+      dist.all_gather_into_tensor(full, part)
+      return full
+
+    def copy_out(m, y):
+      if rank == 0 or not sliced(m):
+        hy[m].copy_(y, non_blocking=True)
+
     def e2e_pass(m):
-      xd = hx[m].to(dev, non_blocking=True)
-      y = wl.forward(m, x=xd)
-      hy[m].copy_(y, non_blocking=True)
+      y = wl.forward(m, x=copy_in(m))
+      copy_out(m, y)
 
     # the small batches are launch-bound from Python: their passes (copy in, three linears, exchange, copy out) are
     # captured once and replayed, which any user of the operators can do; M = 512 is launched eagerly
@@ -596,17 +617,55 @@ def run_ours(args, rank, world, local_rank):
           for _ in range(e2e_reps):
             e2e_pass(m)
         e2e_graphs[m] = eg
+        eg = None  # the dict holds the only reference: teardown has to be able to drop every graph
       except Exception as e:
         torch.cuda.synchronize(dev)
         print(f"[bench] end-to-end pass at M={m} not captured ({type(e).__name__}: {e}); launched eagerly", file=sys.stderr)
+
+    # Eagerly launched passes (M = 512) move their copies to two side streams: the activations of pass r + 1 come in
+    # while pass r computes, its result goes out under pass r + 1 - what a serving loop over the operators does.
+    cp_in, cp_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    xin = {m: [torch.empty(m, H, dtype=torch.bfloat16, device=dev) for _ in range(2)] for m in MS if m not in e2e_graphs}
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_free = [torch.cuda.Event() for _ in range(2)]
+    ev_out_done = torch.cuda.Event()
+
+    def e2e_passes_overlapped(m):
+      for r in range(e2e_reps):
+        b = r & 1
+        if sliced(m):
+          # the gather is a collective: it stays on the compute stream, in program order with the exchange
+          with torch.cuda.stream(cp_in):
+            part = hx[m][rank * (m // world):(rank + 1) * (m // world)].to(dev, non_blocking=True)
+            ev_in[b].record(cp_in)
+          stream.wait_event(ev_in[b])
+          dist.all_gather_into_tensor(xin[m][b], part)
+          part.record_stream(stream)
+        else:
+          with torch.cuda.stream(cp_in):
+            if r >= 2:
+              cp_in.wait_event(ev_free[b])  # the pass that read this buffer has finished with it
+            xin[m][b].copy_(hx[m], non_blocking=True)
+            ev_in[b].record(cp_in)
+          stream.wait_event(ev_in[b])
+        y = wl.forward(m, x=xin[m][b])
+        ev_free[b].record(stream)
+        ev_y = torch.cuda.Event()
+        ev_y.record(stream)
+        if rank == 0 or not sliced(m):
+          with torch.cuda.stream(cp_out):
+            cp_out.wait_event(ev_y)
+            hy[m].copy_(y, non_blocking=True)
+            y.record_stream(cp_out)
+      ev_out_done.record(cp_out)
+      stream.wait_event(ev_out_done)
 
     def e2e_step():
       for m in MS:
         if m in e2e_graphs:
           e2e_graphs[m].replay()
         else:
-          for _ in range(e2e_reps):
-            e2e_pass(m)
+          e2e_passes_overlapped(m)
       stream.synchronize()  # every result of the step is in its host buffer
 
     for _ in range(3):
@@ -674,8 +733,11 @@ def run_ours(args, rank, world, local_rank):
                                f"{dom_us:.1f} us per launch, {len(gate_up_us)} launches timed",
                      "algorithmic_flops_per_launch": dom_flops},
         "per_batch": per_m,
-        "e2e": {"value": e2e_tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": e2e_reps * sum(2 * m * H for m in MS),
-                "d2h_bytes_per_step": e2e_reps * sum(2 * m * H for m in MS)},
+        "e2e": {"value": e2e_tokens / (e2e_ms * 1e-3), "unit": "tokens/s",
+                "h2d_bytes_per_step": e2e_reps * sum(2 * (m // world if world > 1 and m % world == 0 else m) * H for m in MS),
+                "d2h_bytes_per_step": e2e_reps * sum(2 * m * H for m in MS),
+                "how": "pinned host activations in, pinned host result out, every pass; with N GPUs each rank copies in a 1/N "
+                       "slice of the batch and the ranks all-gather it over NVLink, rank 0 reads the result (bytes are rank 0's)"},
         "gpu_launches": args.steps * reps * sum(launches_per_pass.values()),
         "clocks": clocks,
         "tp": {"G": world, "checked": checked},
@@ -684,6 +746,13 @@ def run_ours(args, rank, world, local_rank):
     if not args.no_cpu_baseline and world == 1:
       line["cpu_baseline"] = cpu_sample(args.seed)
     print(json.dumps(line), flush=True)
+  # The line is out.  Teardown of the process group has blocked before when something still held a captured
+  # communicator; a rank that cannot finish it within half a minute leaves anyway.
+  if world > 1:
+    sys.stdout.flush()
+    watchdog = threading.Timer(30.0, lambda: os._exit(0))
+    watchdog.daemon = True
+    watchdog.start()
   # captured graphs hold the communicator and the peer buffers: they go first
   graphs.clear()
   e2e_graphs.clear()

@@ -57,6 +57,18 @@ def test_argument_errors_need_no_gpu():
   # fused gate/up: the interleaved weight has a multiple of 16 rows
   assert L.qmm_gate_up_decode(4, 1, 1, 1, 1, 1, 1, 1, 24, 128, 0, None) == 1
   assert b"multiple of 16" in L.qmm_last_error_string()
+  assert L.qmm_gate_up(4, 1, 1, 1, 1, 1, 1, 64, 24, 128, 0, None, 0, None) == 1
+  assert b"multiple of 16" in L.qmm_last_error_string()
+  # scratch of the weight-only entry point: grows with the batch, never shrinks; the int4 form adds room for the
+  # weights as int8 from 384 tokens
+  sizes = [L.qmm_weight_only_workspace_size(m, 4096) for m in (1, 16, 32, 33, 64, 65, 512, 1008, 1024, 4096)]
+  assert all(a <= b for a, b in zip(sizes, sizes[1:])) and sizes[0] > 0
+  assert L.qmm_weight_only_workspace_size_for(8, 512, 14336, 4096) == L.qmm_weight_only_workspace_size(512, 4096)
+  assert L.qmm_weight_only_workspace_size_for(4, 64, 14336, 4096) == L.qmm_weight_only_workspace_size(64, 4096)
+  assert L.qmm_weight_only_workspace_size_for(4, 512, 14336, 4096) >= L.qmm_weight_only_workspace_size(512, 4096) + 14336 * 4096
+  # limbs per activation: by output type (0) or three everywhere (3)
+  assert L.qmm_set_activation_limbs(3) == 0 and L.qmm_set_activation_limbs(0) == 0
+  assert L.qmm_set_activation_limbs(2) == 1
   # exchange buffers of the fused row-parallel kernel: two slots of `world` regions, one flag word per rank and tile
   world, max_m, n = 8, 8, 8192
   want = 2 * world * max_m * n * 4 + (world * (n // 16) + 2) * 4
