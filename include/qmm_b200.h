@@ -146,9 +146,9 @@ QMM_API int qmm_w8a16_blockwise(const void* x, int x_dtype, const int8_t* w, con
  *   1024 bytes are ZERO before the first call (the kernel leaves them zero); calls that share a workspace must be
  *   ordered on the GPU (same stream).  NULL / 0 is allowed and rules the I8TC variant out.  A workspace of
  *   qmm_weight_only_workspace_size_for(wbits, max M, N, K) bytes additionally lets long int4 batches (384 tokens
- *   and more per channel, 768 with scale blocks) expand the weights to int8 once per call (N*K bytes behind the
+ *   and more per channel, 512 with scale blocks) expand the weights to int8 once per call (N*K bytes behind the
  *   regular scratch; with less room they are expanded in slices of rows, or per tile inside the kernel as for short
- *   batches): 1.2x faster at 512 tokens per channel, 1.1-1.3x at 1024.  Results are bit-identical either way.
+ *   batches): 1.2x faster at 512 tokens per channel (1.05x with scale blocks), 1.1-1.3x at 1024.  Results are bit-identical either way.
  * I8TC computes  sum_k X[m,k] * w[n,k]  exactly in int32, where X is the activation row in 22-bit fixed point
  * relative to the row's largest exponent (exact for bf16/f16 values within 2^-14 of the row maximum, rounded at
  * 2^-22 of it below), then applies scales in fp32: the accuracy of an fp32 accumulation.  (16-bit outputs above 32

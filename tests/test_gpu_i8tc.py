@@ -141,7 +141,7 @@ def _abi_int4(x, wp, s, bs, out_dtype, ws_bytes):
   return out
 
 
-# long int4 batches (384 tokens per channel, 768 with scale blocks): the weights are expanded to int8 once when the
+# long int4 batches (384 tokens per channel, 512 with scale blocks): the weights are expanded to int8 once when the
 # workspace has room (all of them, or slices of rows), per tile inside the kernel otherwise; the three routes add the
 # same integers in the same order
 @pytest.mark.parametrize("M,out_dtype", [(400, torch.float32), (512, torch.bfloat16), (800, torch.bfloat16), (1100, torch.bfloat16),

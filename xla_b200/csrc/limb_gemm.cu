@@ -1143,7 +1143,7 @@ namespace {
 
 // int4 batches at least this long are expanded to int8 once when the caller gave room: the pass over the weights is
 // paid back sooner per channel (the int8 form then runs with no hand-over inside a tile) than with scale blocks
-constexpr int64_t kExpandTokens = 384, kExpandTokensBlockwise = 768;
+constexpr int64_t kExpandTokens = 384, kExpandTokensBlockwise = 512;
 
 // Work split of one token tile.  Stream-K (equal shares of the tile x K-slot units) keeps every SM streaming, but a
 // tile shared by several CTAs costs a partial-tile exchange through L2 at the end of the kernel, worth a few slots of
