@@ -67,6 +67,7 @@ namespace {
 #define DBG_BEGIN() dbg_t = clock64()
 #define DBG_END(i) dbg_w[i] += clock64() - dbg_t
 #define DBG_STAMP(i) if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) g_limb_dbg[42 + (i)] = (long long)ptx::globaltimer_ns()
+#define DBG_STAMP1(i) if (blockIdx.x == 1 && (threadIdx.x & 31) == 0) g_limb_dbg[42 + (i)] = (long long)ptx::globaltimer_ns()
 #define DBG_FLUSH(base)                                                  \
   if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) {                      \
     for (int i_ = 0; i_ < 4; ++i_) g_limb_dbg[(base) + i_] = dbg_w[i_];  \
@@ -77,6 +78,7 @@ namespace {
 #define DBG_BEGIN()
 #define DBG_END(i)
 #define DBG_STAMP(i)
+#define DBG_STAMP1(i)
 #define DBG_FLUSH(base)
 #endif
 
@@ -737,6 +739,9 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS, NL>::kThreads, Cfg<WBITS, NC
     int tile, u0, u1, buf = 0;
     uint32_t pacc = 0;
     __shared__ int s_npart, s_ready;
+    __shared__ float s_pw[2][64];
+    static_assert(MT <= 64, "per-token factors of a tile");
+    int frag = 0;
     auto wait_acc = [&]() {
       DBG_BEGIN();
       ptx::mbar_wait_warp<32>(&acc_full[buf], pacc, abort_flag, p.err_word, ptx::kErrWaitTmemFull);
@@ -758,6 +763,13 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS, NL>::kThreads, Cfg<WBITS, NC
       const bool first = u0 == 0, last = u1 == p.ut;
       const int mt0 = it.y * MT + half * MTD;  // first token this thread owns (0 outside item mode)
       const int mcount = p.M - mt0;          // tokens from there to the end of the batch
+      // What the final store needs from global memory is fetched now, under the K loop: the per-channel scale into a
+      // register, the tile's per-token factors into shared memory (two buffers: a fragment's barrier separates the
+      // readers of one from the writers of its next use).  Fetched at the end they are two L2 round trips per tile.
+      float* pw_s = s_pw[frag & 1];
+      ++frag;
+      const float ps = (p.mode != kPerChannel || !n_ok || !first) ? 1.f : __ldg(p.scale + n);
+      if (first && dt < MT) pw_s[dt] = it.y * MT + dt < p.M ? __ldg(p.pw + it.y * MT + dt) : 0.f;
       float total[MTD];
 #pragma unroll
       for (int t = 0; t < MTD; ++t) total[t] = 0.f;
@@ -882,15 +894,23 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS, NL>::kThreads, Cfg<WBITS, NC
       if (!first) {
         // a later K range of a tile that another CTA started: leave the partial sums for that CTA
         float* dst = p.partial + ((size_t)blockIdx.x * MT + half * MTD) * BMW + rl;
+        if (warp == kDrainWarp0) { DBG_STAMP1(18); }
 #pragma unroll
         for (int t = 0; t < MTD; ++t)
           if (t < mcount) __stcg(dst + t * BMW, total[t]);
-        __threadfence();
+        if (warp == kDrainWarp0) { DBG_STAMP1(19); }
+        // the barrier orders every drain thread's stores before thread 0's release, which is cumulative at GPU scope
         drain_bar();
-        if (dt == 0) st_release_gpu(p.flags + blockIdx.x, 1u);
+        if (warp == kDrainWarp0) { DBG_STAMP1(20); }
+        if (dt == 0) {
+          __threadfence();
+          st_release_gpu(p.flags + blockIdx.x, 1u);
+        }
+        if (warp == kDrainWarp0) { DBG_STAMP1(21); }
         DBG_END(2);
         continue;
       }
+      if (warp == kDrainWarp0) { DBG_STAMP(14); }
       if (!last && !fetched) {
         // add the partial sums of the CTAs that continue the tile, in CTA order
         for (int j = dt; j < np; j += kDT) {
@@ -906,19 +926,24 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS, NL>::kThreads, Cfg<WBITS, NC
           }
         }
         drain_bar();
+        if (warp == kDrainWarp0) { DBG_STAMP(15); }
         add_partials();
+        if (warp == kDrainWarp0) { DBG_STAMP(16); }
       }
-      const float ps = (p.mode != kPerChannel || !n_ok) ? 1.f : __ldg(p.scale + n);
+      drain_bar();  // the factors written at the top of the fragment are visible
+      float pwv[MTD];
+#pragma unroll
+      for (int t = 0; t < MTD; ++t) pwv[t] = pw_s[half * MTD + t];
       if (!p.gate_up) {
 #pragma unroll
         for (int t = 0; t < MTD; ++t)
           if (t < mcount && n_ok)
-            store_from_f32(p.out, (int64_t)(p.m0 + mt0 + t) * p.ld + n, p.out_dt, total[t] * ps * __ldg(p.pw + mt0 + t));
+            store_from_f32(p.out, (int64_t)(p.m0 + mt0 + t) * p.ld + n, p.out_dt, total[t] * ps * pwv[t]);
       } else {
         // rows come in groups of 16: eight gate rows, then the eight up rows of the same outputs
 #pragma unroll
         for (int t = 0; t < MTD; ++t) {
-          const float v = t < mcount ? total[t] * ps * __ldg(p.pw + mt0 + t) : 0.f;
+          const float v = t < mcount ? total[t] * ps * pwv[t] : 0.f;
           const float u = __shfl_down_sync(0xffffffffu, v, 8);
           if (t < mcount && n_ok && (rl & 8) == 0)
             store_from_f32(p.out, (int64_t)(p.m0 + mt0 + t) * (p.ld >> 1) + gate_up_column(n), p.out_dt, silu_mul(v, u));
@@ -1104,14 +1129,7 @@ int launch_cfg(const CUtensorMap& map_w, const CUtensorMap& map_x, const Params&
 
 template <int WBITS>
 int launch_ncols(int ncols, int nl, const CUtensorMap& map_w, const CUtensorMap& map_x, const Params& p, int grid, cudaStream_t st) {
-  if (nl == 2) {
-    switch (ncols) {
-      case 16: return launch_cfg<WBITS, 16, 2>(map_w, map_x, p, grid, st);
-      case 32: return launch_cfg<WBITS, 32, 2>(map_w, map_x, p, grid, st);
-      case 64: return launch_cfg<WBITS, 64, 2>(map_w, map_x, p, grid, st);
-      default: return launch_cfg<WBITS, 128, 2>(map_w, map_x, p, grid, st);
-    }
-  }
+  if (nl == 2) return launch_cfg<WBITS, 128, 2>(map_w, map_x, p, grid, st);
   switch (ncols) {
     case 16: return launch_cfg<WBITS, 16>(map_w, map_x, p, grid, st);
     case 32: return launch_cfg<WBITS, 32>(map_w, map_x, p, grid, st);
@@ -1179,34 +1197,6 @@ Split split_one_tile(int wbits, const Plan& pl, long long tiles, long long slots
     while (tiles % sp.grid != 0) --sp.grid;
   }
   return sp;
-}
-
-// Few weight tiles (a narrow layer, a tensor-parallel shard): with the widest token tile only `tiles` CTAs would get a
-// whole-K item, and splitting K instead costs the exchange, which grows with the tile.  Narrower token tiles give
-// more CTAs a whole-K item each (an MMA costs the same for any width up to 128 columns, and the tensor pipe is idle
-// here anyway); the weight tile is then read by several CTAs, from L2.
-void narrow_for_few_tiles(Plan& pl, int wbits, int64_t M, int64_t N, int64_t K, int64_t block_size) {
-  const long long tiles = ceil_div(N, BMW), sms = sm_count(), slots = ceil_div(K, kSlotK);
-  const long long y0 = pl.items ? ceil_div(M, pl.tile_tokens) : 1;
-  if (tiles * y0 * 4 >= sms * 3) return;  // most SMs have an item already
-  static const int w3[] = {128, 96, 48, 32, 16}, w2[] = {128, 64, 32, 16};
-  const int* ws = pl.nl == 2 ? w2 : w3;
-  const int nw = pl.nl == 2 ? 4 : 5;
-  int pick = 0;
-  for (int i = 0; i < nw; ++i) {
-    if (ws[i] > pl.ncols) continue;
-    pick = ws[i];
-    if (tiles * ceil_div(M, ws[i] / pl.nl) * 4 >= sms * 3) break;
-  }
-  const long long y = ceil_div(M, pick / pl.nl);
-  if (pick == 0 || y <= y0) return;  // no narrower tile gives more items
-  const long long cand = ceil_div(tiles * y, sms) * slots;
-  const int spu = (block_size > 0 && block_size != kTileK) ? (int)(block_size / kSlotK) : 1;
-  const long long base = pl.items ? ceil_div(tiles * y0, sms) * slots : split_one_tile(wbits, pl, tiles, slots, spu).cost;
-  if (cand >= base) return;
-  pl.ncols = pick;
-  pl.tile_tokens = pick / pl.nl;
-  pl.items = true;
 }
 
 // One launch of the main kernel over `rows` weight rows at `w` (row pitch K * wbits / 8 bytes).
@@ -1301,8 +1291,7 @@ int launch_limb_impl(int wbits, const void* x, int x_dt, const void* w, const fl
                 wbits == 8 ? 16 : 32, (long long)M, (long long)N, (long long)K, (long long)block_size);
   if (gate_up && N % 16 != 0)
     return fail(QMM_ERR_BAD_SHAPE, "fused gate/up epilogue: the interleaved weight needs a multiple of 16 rows, got %lld", (long long)N);
-  Plan pl = plan_for(wbits, M, out_dt);
-  if (M <= max_rows(pl.nl)) narrow_for_few_tiles(pl, wbits, M, N, K, block_size);
+  const Plan pl = plan_for(wbits, M, out_dt);
   const int nl = pl.nl;
   const size_t need = carve(nullptr, std::min(M, max_rows(nl)), K, nl, pl.items ? 0 : pl.tile_tokens, kLimbMaxCtas).bytes;
   if (!workspace || workspace_bytes < need)
@@ -1451,6 +1440,9 @@ extern "C" __attribute__((visibility("default"))) void qmm_debug_limb_dump() {
     for (int i = 0; i < n; ++i) { mx = std::max(mx, (c[4 * i + 3] - t0) * 1e-3); mxe = std::max(mxe, (c[4 * i] - t0) * 1e-3); }
     fprintf(stderr, "[dbg]   %d CTAs, last entry %.2f, last exit %.2f\n", n, mxe, mx);
   }
+  fprintf(stderr, "[dbg] exchange (us after CTA 0's entry): owner CTA 0: K loop folded %.2f | flags seen %.2f | partials added %.2f | stored %.2f || CTA 1: partial ready %.2f | stored %.2f | fenced %.2f | flag set %.2f\n",
+          (h[56] - h[42]) * 1e-3, (h[57] - h[42]) * 1e-3, (h[58] - h[42]) * 1e-3, (h[48] - h[42]) * 1e-3, (h[60] - h[42]) * 1e-3,
+          (h[61] - h[42]) * 1e-3, (h[62] - h[42]) * 1e-3, (h[63] - h[42]) * 1e-3);
   fprintf(stderr, "[dbg] kernel  cycles=%lld ns=%lld -> %.3f GHz\n", h[40], h[41], h[41] ? (double)h[40] / (double)h[41] : 0.0);
 }
 #endif
