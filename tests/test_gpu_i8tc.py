@@ -168,6 +168,27 @@ def test_int4_widened_once_matches_in_kernel_expansion(M, out_dtype, bs):
   assert qo.max_abs_rel(direct, _exact(x.cpu(), w, s, bs)) < tol
 
 
+# 160 items (20 weight tiles x 8 token tiles) on 148 SMs: the partly filled second round is avoided by dealing the
+# (item, K unit) space in equal shares; items that span two CTAs go through the partial-tile exchange
+@pytest.mark.parametrize("bs", [128, 0])
+def test_items_dealt_in_equal_shares(bs):
+  from xla_b200 import _capi
+  g = qc.gen(900 + bs)
+  M, N, K = 512, 2560, 8192
+  x = qc.activations(g, M, K, outliers=True)
+  w = qc.int4_weight(g, N, K)
+  s = qc.blockwise_scale(g, K // bs, N) if bs > 0 else qc.per_channel_scale(g, N)
+  wp = xla_b200.pack_int4(w.to(DEV))
+  base = _capi.lib().qmm_weight_only_workspace_size(M, K)   # no room to widen: the int4 instance runs
+  outs = [_abi_int4(x.to(DEV), wp, s.to(DEV), bs, torch.bfloat16, base) for _ in range(3)]
+  assert torch.equal(outs[1], outs[0]) and torch.equal(outs[2], outs[0])
+  rows = torch.cat([torch.arange(0, 6), torch.arange(60, 70), torch.arange(250, 260), torch.arange(505, 512)])
+  exact = _exact(x[rows], w, s, bs)
+  assert qo.max_abs_rel(outs[0][rows], exact) < TOL_BF16
+  out32 = _abi_int4(x.to(DEV), wp, s.to(DEV), bs, torch.float32, base)   # three limbs: 13 token tiles
+  assert qo.max_abs_rel(out32[rows], exact) < TOL_F32
+
+
 @pytest.mark.parametrize("xdt", [torch.float32, torch.float16, torch.bfloat16])
 def test_activation_dtypes_and_ranges(xdt):
   g = qc.gen(7)
@@ -206,7 +227,12 @@ def test_deterministic_and_workspace_left_clean():
   g = qc.gen(11)
   M, N, K = 16, 384, 8192   # three tiles over all SMs: every tile is summed from many partial tiles
   x, w, s = qc.activations(g, M, K), qc.int8_weight(g, N, K), qc.per_channel_scale(g, N)
-  outs = [_run(x, w, s, 0, 8, torch.float32) for _ in range(10)]
+  # (other work between the runs shifts the timing of the partial tiles; the sums must not depend on when they land)
+  outs = []
+  for i in range(30):
+    outs.append(_run(x, w, s, 0, 8, torch.float32))
+    if i % 3 == 0:
+      torch.zeros(1 << 22, device=DEV).sum()
   for o in outs[1:]:
     assert torch.equal(o, outs[0])
   assert qo.max_abs_rel(outs[0], _exact(x, w, s, 0)) < TOL_F32

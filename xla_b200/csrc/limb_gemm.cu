@@ -34,6 +34,7 @@
 // Weight bytes in flight per SM = the depth of the TMA ring (64-190 KB), independent of registers and occupancy.
 #include <algorithm>
 #include <atomic>
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
 
@@ -111,7 +112,12 @@ struct Params {
   uint32_t* flags;  // [grid], zero between launches
   uint32_t* err_word;
   int gate_up;
-  int ytiles;  // > 0: work items are (weight tile, token tile) pairs with the whole K range each; 0: stream-K
+  int ytiles;    // token tiles per weight tile (1 up to one tile's tokens); a work item is a (weight tile, token tile) pair
+  // The schedule: the first `items1` items go to the CTAs whole (CTA c takes items c, c + G, ...); the K units of
+  // the remaining items (`units` of them) are dealt in equal contiguous shares to the first `g2` CTAs (stream-K: an
+  // item that spans CTAs is summed through the partial tiles).  One token tile: items1 = 0, g2 = the grid.
+  long long items1;
+  int g2;
   int m0;      // first token of this launch inside the caller's batch (row offset of `out`)
 };
 
@@ -162,37 +168,37 @@ struct Cfg {
   static_assert(kSmem <= (kOcc == 2 ? 110 * 1024 : 227 * 1024), "shared memory budget");
 };
 
-// The (tile, unit range) fragments of this CTA's share of the stream-K schedule, in order.
+// The (item, unit range) fragments of this CTA's share of the schedule, in order.  Item i = (weight tile i / ytiles,
+// token tile i % ytiles): the token tiles of one weight tile are neighbours in the order, run on neighbouring CTAs at
+// the same time and share the tile's bytes in L2.
 struct FragIter {
-  long long u, hi;
+  long long u, hi;        // this CTA's range of the dealt units (counted from the first dealt item)
   int ut;
-  int ytiles, y;          // item mode: number of token tiles, token tile of the current item
-  long long item, items;
-  __device__ FragIter(const Params& p) : ut(p.ut), ytiles(p.ytiles), y(0) {
-    const long long G = gridDim.x;
-    u = (long long)blockIdx.x * p.units / G;
-    hi = (long long)(blockIdx.x + 1) * p.units / G;
-    item = blockIdx.x;
-    items = (long long)p.tiles * p.ytiles;
+  int ytiles, y;          // number of token tiles, token tile of the current item
+  long long item;         // the current fragment's item once next() returned true
+  long long nxt, items1;  // whole items: the next one of this CTA, their number
+  __device__ FragIter(const Params& p) : ut(p.ut), ytiles(p.ytiles), y(0), item(0), nxt(blockIdx.x), items1(p.items1) {
+    const long long c = blockIdx.x;
+    u = c < p.g2 ? c * p.units / p.g2 : 0;
+    hi = c < p.g2 ? (c + 1) * p.units / p.g2 : 0;
   }
   __device__ bool next(int& tile, int& u0, int& u1) {
-    if (ytiles) {
-      // Large batches: item i = (weight tile i / ytiles, token tile i % ytiles), CTA c takes items c, c + G, ...;
-      // the token tiles of one weight tile run on neighbouring CTAs at the same time and share its bytes in L2.
-      if (item >= items) return false;
-      tile = (int)(item / ytiles);
-      y = (int)(item - (long long)tile * ytiles);
+    if (nxt < items1) {
+      item = nxt;
+      nxt += gridDim.x;
       u0 = 0;
       u1 = ut;
-      item += gridDim.x;
-      return true;
+    } else {
+      if (u >= hi) return false;
+      const long long rel = u / ut;
+      item = items1 + rel;
+      u0 = (int)(u - rel * ut);
+      const long long rem = hi - u;
+      u1 = (int)(rem < (long long)(ut - u0) ? u0 + rem : ut);
+      u += u1 - u0;
     }
-    if (u >= hi) return false;
-    tile = (int)(u / ut);
-    u0 = (int)(u - (long long)tile * ut);
-    const long long rem = hi - u;
-    u1 = (int)(rem < (long long)(ut - u0) ? u0 + rem : ut);
-    u += u1 - u0;
+    tile = (int)(item / ytiles);
+    y = (int)(item - (long long)tile * ytiles);
     return true;
   }
 };
@@ -733,12 +739,11 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS, NL>::kThreads, Cfg<WBITS, NC
     const int dt = half ? 128 + (int)threadIdx.x - C::kXDrainWarp0 * 32 : (int)threadIdx.x - kDrainWarp0 * 32;  // 0..kDT-1
     auto drain_bar = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(kDT) : "memory"); };
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-    const long long G = gridDim.x;
     FragIter it(p);
     DBG_DECL;
     int tile, u0, u1, buf = 0;
     uint32_t pacc = 0;
-    __shared__ int s_npart, s_ready;
+    __shared__ int s_npart;
     __shared__ float s_pw[2][64];
     static_assert(MT <= 64, "per-token factors of a tile");
     int frag = 0;
@@ -773,11 +778,9 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS, NL>::kThreads, Cfg<WBITS, NC
       float total[MTD];
 #pragma unroll
       for (int t = 0; t < MTD; ++t) total[t] = 0.f;
-      // A tile this CTA starts and others continue: their partial sums are usually there already (every CTA works on
-      // its share of a started tile first), so they are fetched now, under the K loop, when all of them have landed;
-      // otherwise after it.  The order of the additions is the same either way.
+      // A tile this CTA starts and others continue: their partial sums are added after this CTA's own K range, in
+      // CTA order - always in that order, whenever they land, so that the result does not depend on timing.
       int np = 0;
-      bool fetched = false;
       auto add_partials = [&]() {
         // two partial tiles in flight at a time (an L2 round trip each), added in CTA order
         const float* src = p.partial + ((size_t)(blockIdx.x + 1) * MT + half * MTD) * BMW + rl;
@@ -804,20 +807,14 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS, NL>::kThreads, Cfg<WBITS, NC
       if (first && !last) {
         if (dt == 0) {
           int cnt = 0;
-          for (long long c2 = blockIdx.x + 1; c2 < G; ++c2) {
-            if (c2 * p.units / G >= (long long)(tile + 1) * p.ut) break;
+          for (long long c2 = blockIdx.x + 1; c2 < p.g2; ++c2) {
+            if (c2 * p.units / p.g2 >= (it.item - p.items1 + 1) * p.ut) break;
             ++cnt;
           }
           s_npart = cnt;
-          s_ready = 1;
         }
         drain_bar();
         np = s_npart;
-        for (int j = dt; j < np; j += kDT)
-          if (ld_acquire_gpu(p.flags + blockIdx.x + 1 + j) == 0u) s_ready = 0;
-        drain_bar();
-        fetched = s_ready != 0;
-        if (fetched) add_partials();
       }
       // block scales are fetched four blocks ahead: a load issued in the iteration that uses it would put an L2
       // round trip into every block's drain
@@ -911,7 +908,7 @@ __global__ void __launch_bounds__(Cfg<WBITS, NCOLS, NL>::kThreads, Cfg<WBITS, NC
         continue;
       }
       if (warp == kDrainWarp0) { DBG_STAMP(14); }
-      if (!last && !fetched) {
+      if (!last) {
         // add the partial sums of the CTAs that continue the tile, in CTA order
         for (int j = dt; j < np; j += kDT) {
           const uint32_t* f = p.flags + blockIdx.x + 1 + j;
@@ -1080,7 +1077,7 @@ Plan plan_for(int wbits, int64_t M, int out_dt) {
 int64_t max_rows(int nl) { return nl == 2 ? 1024 : 1008; }
 
 // Layout of the caller's scratch: [flags: 1 KB][pw][limbs][partial tiles]; the flag words come first so that a
-// caller who clears only the head of the buffer clears them.  partial_tokens: tokens of a stream-K tile, 0 for items.
+// caller who clears only the head of the buffer clears them.  partial_tokens: tokens of a token tile.
 Scratch carve(void* base, int64_t M, int64_t K, int nl, int partial_tokens, int max_ctas) {
   Scratch s;
   uint8_t* b = reinterpret_cast<uint8_t*>(base);
@@ -1204,14 +1201,37 @@ int launch_main(int wbits, const void* w, int64_t rows, int64_t K, const Plan& p
   const int ncols = pl.ncols;
   p.N = rows;
   p.tiles = (int)ceil_div(rows, BMW);
-  p.units = (long long)p.tiles * p.ut;
   int grid;
   if (pl.items) {
-    // the CTAs walk the (weight tile, token tile) items; nothing is exchanged between them
+    // the CTAs walk the (weight tile, token tile) items, whole items each: nothing is exchanged between them
     const int occ = (wbits == 4 && ncols <= 48) ? 2 : 1;  // Cfg::kOcc
-    grid = (int)std::min<long long>((long long)occ * sm_count(), (long long)p.tiles * p.ytiles);
+    const long long items = (long long)p.tiles * p.ytiles, ctas = (long long)occ * sm_count();
+    grid = (int)std::min<long long>(ctas, items);
+    p.items1 = items;
+    p.units = 0;
+    p.g2 = 0;
+    // A partly filled last round (448 items on 148 SMs are four rounds for three rounds' work): the items of that
+    // round are split along K over a few CTAs each instead, and summed through the partial tiles like a stream-K
+    // tile.  Splitting an item over s CTAs costs item/s plus an exchange that grows with s (one partial tile per
+    // CTA, read by the item's first CTA); times in microseconds, per-slot figures measured.
+    const long long left = items % ctas;
+    if (items > ctas && left != 0) {
+      const double item_us = (double)p.slots * (wbits == 4 ? 1.1 : (p.mode == kPerChannel ? 0.55 : 0.9));
+      const double per_partial_us = 0.7 * pl.tile_tokens / 64.0;
+      double s = std::sqrt(item_us / per_partial_us);  // CTAs per item; need not be whole: the units are dealt evenly
+      s = std::min(s, std::min((double)ctas / (double)left, (double)p.ut));
+      if (s >= 1.5 && item_us / s + 3.0 + per_partial_us * s < 0.75 * item_us) {
+        p.items1 = items - left;
+        p.units = left * p.ut;
+        p.g2 = (int)std::min<long long>(ctas, (long long)((double)left * s));
+      }
+    }
   } else {
-    grid = split_one_tile(wbits, pl, p.tiles, p.slots, p.spu).grid;
+    const Split sp = split_one_tile(wbits, pl, p.tiles, p.slots, p.spu);
+    grid = sp.grid;
+    p.items1 = 0;
+    p.units = (long long)p.tiles * p.ut;
+    p.g2 = grid;
   }
   CUtensorMap map_w;
   const int rc = encode_tmap_2d(&map_w, w, 1, false, (uint64_t)rows, (uint64_t)(K * wbits / 8), BMW, 128);
@@ -1293,7 +1313,7 @@ int launch_limb_impl(int wbits, const void* x, int x_dt, const void* w, const fl
     return fail(QMM_ERR_BAD_SHAPE, "fused gate/up epilogue: the interleaved weight needs a multiple of 16 rows, got %lld", (long long)N);
   const Plan pl = plan_for(wbits, M, out_dt);
   const int nl = pl.nl;
-  const size_t need = carve(nullptr, std::min(M, max_rows(nl)), K, nl, pl.items ? 0 : pl.tile_tokens, kLimbMaxCtas).bytes;
+  const size_t need = carve(nullptr, std::min(M, max_rows(nl)), K, nl, pl.tile_tokens, kLimbMaxCtas).bytes;
   if (!workspace || workspace_bytes < need)
     return fail(QMM_ERR_WORKSPACE, "split-activation tensor-core kernel needs %zu bytes of workspace, got %zu", need, workspace_bytes);
   if (!aligned(workspace, 256)) return fail(QMM_ERR_MISALIGNED, "workspace must be 256-byte aligned");
@@ -1324,7 +1344,7 @@ int launch_limb_impl(int wbits, const void* x, int x_dt, const void* w, const fl
     }
     return QMM_OK;
   }
-  const Scratch sc = carve(workspace, M, K, nl, pl.items ? 0 : pl.tile_tokens, kLimbMaxCtas);
+  const Scratch sc = carve(workspace, M, K, nl, pl.tile_tokens, kLimbMaxCtas);
 
   // slices of weight rows that fit behind the scratch, expanded and multiplied one after the other
   int64_t slice_rows = 0;
@@ -1373,7 +1393,7 @@ int launch_limb_impl(int wbits, const void* x, int x_dt, const void* w, const fl
   p.flags = sc.flags;
   p.err_word = device_error_word();
   p.gate_up = gate_up;
-  p.ytiles = pl.items ? (int)ceil_div(M, pl.tile_tokens) : 0;
+  p.ytiles = pl.items ? (int)ceil_div(M, pl.tile_tokens) : 1;
   p.m0 = 0;
   if (slice_rows == 0) {
     p.scale = scale;
