@@ -189,6 +189,20 @@ def test_items_dealt_in_equal_shares(bs):
   assert qo.max_abs_rel(out32[rows], exact) < TOL_F32
 
 
+# one 64-token tile over more weight tiles than SMs: a round of whole tiles, the rest split along K
+@pytest.mark.parametrize("K", [1024, 8192])
+def test_single_wide_tile_over_many_weight_tiles(K):
+  g = qc.gen(950 + K)
+  M, N, bs = 64, 20000, 128
+  x = qc.activations(g, M, K)
+  w = qc.int4_weight(g, N, K)
+  s = qc.blockwise_scale(g, K // bs, N)
+  outs = [_run(x, w, s, bs, 4, torch.bfloat16) for _ in range(3)]
+  assert torch.equal(outs[1], outs[0]) and torch.equal(outs[2], outs[0])
+  rows = torch.tensor([0, 1, 31, 32, 62, 63])
+  assert qo.max_abs_rel(outs[0][rows], _exact(x[rows], w, s, bs)) < TOL_BF16
+
+
 @pytest.mark.parametrize("xdt", [torch.float32, torch.float16, torch.bfloat16])
 def test_activation_dtypes_and_ranges(xdt):
   g = qc.gen(7)

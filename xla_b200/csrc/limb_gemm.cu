@@ -1202,7 +1202,9 @@ int launch_main(int wbits, const void* w, int64_t rows, int64_t K, const Plan& p
   p.N = rows;
   p.tiles = (int)ceil_div(rows, BMW);
   int grid;
-  if (pl.items) {
+  // (one 128-column token tile over more weight tiles than CTAs is scheduled like several: its exchange is too dear
+  // to split every tile, and whole tiles alone leave the last round partly filled)
+  if (pl.items || (ncols == 128 && p.tiles > sm_count())) {
     // the CTAs walk the (weight tile, token tile) items, whole items each: nothing is exchanged between them
     const int occ = (wbits == 4 && ncols <= 48) ? 2 : 1;  // Cfg::kOcc
     const long long items = (long long)p.tiles * p.ytiles, ctas = (long long)occ * sm_count();
