@@ -634,6 +634,34 @@ def test_gate_up_fused_large_batches(M, mode):
   assert qo.max_abs_rel(out, ref.cpu()) < TOL_F32
 
 
+def test_w8a8_outputs_at_odd_offsets():
+  """fp32 `out` and int32 `acc_out` that are only 4-byte aligned (views one element into a buffer): the tensor-core
+  epilogue must fall back from its 16-byte stores and give the same bits as with aligned outputs."""
+  from xla_b200 import _capi
+  L = _capi.lib()
+  g = qc.gen(61)
+  M, N, K = 256, 512, 1024
+  xq = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int8).to(DEV)
+  w = torch.randint(-127, 128, (N, K), generator=g, dtype=torch.int8).to(DEV)
+  ws = qc.per_channel_scale(g, N).to(DEV)
+  xs = (torch.rand(M, generator=g) * 0.05 + 0.01).to(DEV)
+
+  def run(out, acc):
+    with torch.cuda.device(0):
+      _capi.check(L.qmm_w8a8_gemm(_capi.ptr(xq), _capi.ptr(w), _capi.ptr(ws), None, _capi.ptr(xs), None, acc, out, _capi.F32,
+                                  M, N, K, _capi.VARIANTS["tcgen05"], _capi.stream_ptr()))
+      torch.cuda.synchronize()
+
+  out_a = torch.empty(M * N, dtype=torch.float32, device=DEV)
+  acc_a = torch.empty(M * N, dtype=torch.int32, device=DEV)
+  run(out_a.data_ptr(), acc_a.data_ptr())
+  out_b = torch.zeros(M * N + 1, dtype=torch.float32, device=DEV)
+  acc_b = torch.zeros(M * N + 1, dtype=torch.int32, device=DEV)
+  run(out_b.data_ptr() + 4, acc_b.data_ptr() + 4)
+  assert torch.equal(out_b[1:], out_a) and torch.equal(acc_b[1:], acc_a)
+  assert torch.equal(acc_a.view(M, N).cpu(), (xq.cpu().int() @ w.cpu().int().T))
+
+
 def test_concat_projections_qkv():
   """q, k, v read the same activations: one weight stream, outputs split afterwards."""
   g = qc.gen(41)
