@@ -1181,7 +1181,8 @@ Split split_one_tile(int wbits, const Plan& pl, long long tiles, long long slots
   const long long dp_slots = dp_rounds * slots;                               // slots per CTA, whole tiles
   // exchange cost in slots of streaming (measured: ~3 us for tiles of 5 tokens, ~13 us for 64); a partial tile is
   // 128 x tokens floats, so it grows with the tile
-  const long long exchange = (wbits == 4 ? 8 : 4) * (16 + pl.tile_tokens) / 16;
+  // (a slot of the 128-column int4 instance takes three times as long as one of the narrow ones: fewer per exchange)
+  const long long exchange = ((wbits == 4 && pl.ncols == 128) ? 3 : (wbits == 4 ? 8 : 4)) * (16 + pl.tile_tokens) / 16;
   // compare per-SM streaming: with whole tiles only ceil(tiles / rounds) CTAs run, spread over the SMs
   const long long dp_ctas = ceil_div(tiles, dp_rounds);
   const long long dp_per_sm = ceil_div(dp_ctas, sm_count());
