@@ -109,6 +109,33 @@ def test_variant_heuristic_is_shape_only():
   assert L.qmm_variant_for(xla_b200._capi.OP_W8A8_PERCHANNEL, 2048, 4096, 4096, 0, 0) == b"tcgen05"
 
 
+def test_tuned_table_lookup_and_auto_choice():
+  """The measured table (the counterpart of the reference's tuned block sizes, quantized_matmul_kernel.py:326-555)
+  answers every shape family it was generated for, nothing else; AUTO follows it and falls back to the shape rule."""
+  import re
+  from xla_b200 import tune
+  L = xla_b200._capi.lib()
+  known = {0, 3, 4, 6}  # no entry, tcgen05, mma, i8tc
+  for (n, k) in tune.REFERENCE_SHAPES + tune.BENCH_SHAPES:
+    for (wbits, bs) in tune.FORMATS:
+      if (bs and k % bs) or (wbits == 4 and k % 32):
+        continue
+      for m in (1, 2, 3, 8, 16, 32, 33, 64):
+        v = L.qmm_tuned_variant(wbits, m, n, k, bs)
+        assert v in known and v != 0, (wbits, bs, n, k, m, v)
+      assert L.qmm_tuned_variant(wbits, 65, n, k, bs) == 0   # beyond the last batch bucket
+  assert L.qmm_tuned_variant(8, 1, 4097, 4096, 0) == 0     # a shape the tuner never saw
+  # the committed table and the tuner agree on the row format
+  rows = [l for l in open(tune.__file__.replace("tune.py", "csrc/tuned_table.inc")) if l.startswith("{")]
+  assert len(rows) >= 100 and all(re.match(r"\{[48], \d+, \d+, \d+, \{(\d, ){6}\d\}\},", r) for r in rows)
+  # AUTO: table first, shape rule on a miss; zero points rule the split-activation kernel out
+  assert L.qmm_weight_only_variant_for(4, 1, 28672, 8192, 128, 0) == b"i8tc"
+  assert L.qmm_weight_only_variant_for(4, 1, 14336, 4096, 128, 0) == b"mma"
+  assert L.qmm_weight_only_variant_for(8, 512, 4097 * 2, 4096, 0, 0) == b"i8tc"   # shape rule: above 64 tokens
+  assert L.qmm_weight_only_variant_for(8, 1, 4097 * 2, 4096, 0, 0) == b"mma"      # shape rule: a small weight at M = 1
+  assert L.qmm_weight_only_variant_for(8, 1, 28672, 8192, 0, 1) != b"i8tc"
+
+
 def test_rtn_quantizer_layouts_and_reconstruction():
   """quantize_rtn reproduces the reference test helper's layouts (test_quantized_matmul.py:25-74)."""
   from xla_b200 import weight_prep as wp
